@@ -1,0 +1,356 @@
+"""Decode throughput of a stack of NVFP4 MoE layers at conc=1 on 1..8 B200.
+
+    python bench.py --gpus 1 --steps 50 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 50 --warmup 5
+    python bench.py --impl reference --steps 10 --warmup 3      # CPU arm (the oracle port)
+
+A step is one decode token through `--layers` (default 40) MoE blocks of the Inkling-Small
+shape (hidden 4096; 256 NVFP4 experts of width 2048, top-6; 2 shared BF16 experts; router
+258 x 4096) under CUDA-graph replay, experts sharded tensor-parallel on the FFN width with
+one NCCL all-reduce per block. Weights are seeded synthetic N(0, 0.02) quantised to NVFP4
+(no checkpoint offline); every step gets a fresh N(0, 1) activation vector, and the 7.5 GB
+of weights a step streams are far larger than the 126 MB L2. Prints ONE JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for p in (ROOT, ROOT / "tests" / "golden"):
+    if str(p) not in sys.path:
+        sys.path.insert(0, str(p))
+
+HIDDEN, INTERMEDIATE, EXPERTS, N_SHARED, TOP_K = 4096, 2048, 256, 2, 6
+METRIC, UNIT = "decode_tokens_per_s_conc1", "tok/s"
+
+
+def layer_bytes(world: int) -> dict:
+    """Algorithmic bytes one rank streams per block per token."""
+    f = INTERMEDIATE // world
+    gate_up_routed = TOP_K * (2 * f * HIDDEN // 2 + 2 * f * HIDDEN // 16)
+    gate_up_shared = N_SHARED * 2 * f * HIDDEN * 2
+    down_routed = TOP_K * (HIDDEN * f // 2 + HIDDEN * f // 16)
+    down_shared = N_SHARED * HIDDEN * f * 2
+    router = (EXPERTS + N_SHARED) * HIDDEN * 2
+    return dict(gate_up=gate_up_routed + gate_up_shared, down=down_routed + down_shared, router=router,
+                total=gate_up_routed + gate_up_shared + down_routed + down_shared + router + 2 * TOP_K * 4)
+
+
+def resident_bytes_per_layer(world: int) -> int:
+    f = INTERMEDIATE // world
+    expert = 2 * f * HIDDEN // 2 + 2 * f * HIDDEN // 16 + HIDDEN * f // 2 + HIDDEN * f // 16 + 8
+    return EXPERTS * expert + N_SHARED * 3 * f * HIDDEN * 2 + (EXPERTS + N_SHARED) * HIDDEN * 2
+
+
+def load_peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return json.loads(path.read_text()), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi sampled every 200 ms while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(gpu_index)], stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            pass
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        rows = [line.split(", ") for line in Path(self.file.name).read_text().splitlines() if line.strip()]
+        os.unlink(self.file.name)
+        clocks, reasons, sm_max, power = [], set(), None, []
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for row in rows:
+            try:
+                clocks.append(float(row[1]))
+                sm_max = float(row[2])
+                power.append(float(row[3]))
+            except (ValueError, IndexError):
+                continue
+            for name, value in zip(names, row[5:9]):
+                if value.strip().lower() == "active":
+                    reasons.add(name)
+        clocks.sort()
+        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None, "sm_max_mhz": sm_max,
+                "power_w_max": max(power) if power else None, "samples": len(clocks), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------- CPU arm
+def cpu_layer_inputs(seed: int, pool: int = 8):
+    """config[0] on the CPU: router, shared experts and a pool of `pool` NVFP4 experts
+    (the router bias confines the top-6 to the pool, so only those are generated)."""
+    import torch
+
+    import cases
+
+    gen = torch.Generator().manual_seed(seed)
+    p = dict(d=HIDDEN, f=INTERMEDIATE, experts=EXPERTS, n_shared=N_SHARED, top_k=TOP_K, route_scale=8.0)
+    p["router_weight"] = (torch.randn(EXPERTS + N_SHARED, HIDDEN, generator=gen) * 0.02).to(torch.bfloat16)
+    bias = torch.full((EXPERTS,), -10.0)
+    bias[:pool] = 0
+    p["router_bias"] = bias
+    p["global_scale"] = torch.ones(1, dtype=torch.bfloat16)
+    for name, shape in (("shared_gate", (N_SHARED, INTERMEDIATE, HIDDEN)), ("shared_up", (N_SHARED, INTERMEDIATE, HIDDEN)),
+                        ("shared_down", (N_SHARED, HIDDEN, INTERMEDIATE))):
+        p[name] = (torch.randn(*shape, generator=gen) * 0.02).to(torch.bfloat16)
+    banks = cases.make_expert_banks(gen, pool, HIDDEN, INTERMEDIATE)
+    return p, banks, gen
+
+
+def time_cpu_layer(runs: int, warmup: int, seed: int = 0):
+    """Median seconds of one MoE block on the host cores through the oracle's restatement
+    of the reference's PyTorch dequant+matmul path (scripts/run_naive.py:86-108 with
+    my_inkling/model.py:192-226,311-350)."""
+    import torch
+
+    from oracle import moe as oracle_moe
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    p, banks, gen = cpu_layer_inputs(seed)
+    times = []
+    for i in range(warmup + runs):
+        x = torch.randn(1, HIDDEN, generator=gen).to(torch.bfloat16)
+        t0 = time.perf_counter()
+        oracle_moe.moe_layer_reference(x, p, banks)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    times.sort()
+    return times[len(times) // 2], times
+
+
+def run_reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    seconds, times = time_cpu_layer(runs=args.steps, warmup=max(args.warmup, 1))
+    step_ms = 1e3 * sum(times) / len(times) * args.layers
+    value = 1.0 / (sum(times) / len(times) * args.layers)
+    cores = os.cpu_count() or 1
+    sample = (f"{args.steps} timed forwards of ONE block (config[0]) on the host, all {cores} threads; "
+              f"a token is {args.layers} such blocks, so tok/s = 1 / ({args.layers} x mean block time)")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4 weights, bf16 activations, fp32 accumulate",
+        "data": "synthetic", "config": config_dict(args, 1),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def config_dict(args, world: int) -> dict:
+    return {
+        "workload": f"configs[2]: stack of {args.layers} MoE blocks, 1 decode token per step, CUDA-graph replay",
+        "layers": args.layers, "hidden": HIDDEN, "moe_intermediate": INTERMEDIATE, "routed_experts": EXPERTS,
+        "shared_experts": N_SHARED, "top_k": TOP_K, "tokens_per_step": 1,
+        "parallelism": f"tp{world} on the FFN width, 1 all-reduce per block" if world > 1 else "tp1",
+        "l2": "inputs larger than L2: each step streams 7.5 GB of weights, fresh activations per step",
+    }
+
+
+# ---------------------------------------------------------------- GPU arm
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    import inkling_b200 as ib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    group = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+        group = dist.group.WORLD
+
+    # never ask for more memory than is free: shrink the stack instead (and say so)
+    free, total = torch.cuda.mem_get_info()
+    layers = args.layers
+    need = resident_bytes_per_layer(world)
+    reserve = 14 << 30
+    if layers * need > free - reserve:
+        layers = max(1, int((free - reserve) // need))
+    if world > 1:
+        t = torch.tensor([layers], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        layers = int(t.item())
+    args.layers_built = layers
+
+    t_build = time.perf_counter()
+    stack = ib.MoEStack.synthetic(layers, HIDDEN, INTERMEDIATE, EXPERTS, N_SHARED, TOP_K, device, seed=0,
+                                  device_mesh=group, rank=rank, world=world)
+    torch.cuda.synchronize()
+    build_s = time.perf_counter() - t_build
+
+    n_inputs = args.steps + args.warmup
+    gen = torch.Generator().manual_seed(1234)
+    host_x = torch.randn(n_inputs, 1, HIDDEN, generator=gen).to(torch.bfloat16).pin_memory()
+    dev_x = host_x.to(device)
+    host_out = torch.empty(1, HIDDEN, dtype=torch.bfloat16).pin_memory()
+    runner = ib.DecodeStackGraph(stack, dev_x[0], capture=not args.no_graph)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing
+    for i in range(args.warmup):
+        runner.token_in.copy_(dev_x[i])
+        runner.replay()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(args.steps):
+        runner.token_in.copy_(dev_x[args.warmup + i])
+        runner.replay()
+    stop.record()
+    barrier()
+    elapsed_ms = start.elapsed_time(stop)
+    clocks = sampler.stop() if sampler else None
+    if world > 1:
+        t = torch.tensor([elapsed_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+
+    # ---- end to end: pinned host activations in, result back to the host, every step
+    barrier()
+    start.record()
+    for i in range(args.steps):
+        runner.token_in.copy_(host_x[args.warmup + i], non_blocking=True)
+        out = runner.replay()
+        host_out.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()   # conc=1: the next token needs this one
+    stop.record()
+    barrier()
+    e2e_ms = start.elapsed_time(stop)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    finite = bool(torch.isfinite(host_out.float()).all())
+
+    # ---- per-kernel durations for the roofline: one launch per block (distinct weights,
+    # so nothing is L2-warm), events on the launching stream
+    def time_half(half: str, rounds: int = 3) -> float:
+        best = []
+        for _ in range(rounds + 1):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for layer in stack.layers:
+                ex = layer.experts
+                ib.kernels.moe_decode(stack.normed[:1], layer.topk_indices[:1], layer.topk_weights[:1], ex.pointers,
+                                      ex.activated, layer.shared_gate, layer.shared_up, layer.shared_down,
+                                      layer.gammas[:1], layer.shared_activated, layer.partial[:1], ex.max_expert,
+                                      status=ex.status, half=half)
+            b.record()
+            torch.cuda.synchronize()
+            best.append(a.elapsed_time(b) / len(stack.layers))
+        return sum(best[1:]) / rounds   # first round is warm-up
+
+    kernel_ms = {half: time_half(half) for half in ("gate_up", "down")}
+    barrier()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks, peak_kind = load_peaks()
+    bytes_ = layer_bytes(world)
+    dominant = "gate_up"
+    achieved = bytes_[dominant] / (kernel_ms[dominant] * 1e-3) / 1e9
+    tok_s = args.steps / (elapsed_ms * 1e-3)
+    e2e_tok_s = args.steps / (e2e_ms * 1e-3)
+    line = {
+        "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "nvfp4 weights, bf16 activations, fp16 products with fp32 accumulation", "data": "synthetic",
+        "config": config_dict(args, world),
+        "e2e": {"value": e2e_tok_s, "unit": UNIT, "h2d_bytes_per_step": HIDDEN * 2, "d2h_bytes_per_step": HIDDEN * 2},
+        "gpu_launches": args.steps * stack.launches_per_step(),
+        "clocks": clocks,
+        "roofline": {
+            "bound": "hbm", "kernel": "gate_up_kernel<4096> (routed NVFP4 + shared BF16 gate/up GEMV)",
+            "achieved": achieved, "peak": peaks["hbm_gbs"], "peak_kind": peak_kind, "unit": "GB/s",
+            "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+            "algorithmic_bytes_per_launch": bytes_[dominant], "launch_ms": kernel_ms[dominant],
+        },
+        "kernels": {
+            "down_kernel": {"launch_ms": kernel_ms["down"], "algorithmic_bytes": bytes_["down"],
+                            "achieved_gbs": bytes_["down"] / (kernel_ms["down"] * 1e-3) / 1e9},
+            "layer_bytes_per_rank": bytes_["total"],
+            "stack_achieved_gbs": bytes_["total"] * layers * tok_s / 1e9,
+            "stack_frac_of_peak": bytes_["total"] * layers * tok_s / 1e9 / peaks["hbm_gbs"],
+        },
+        "build_seconds": build_s, "layers_built": layers, "output_finite": finite,
+    }
+    if layers != args.layers:
+        line["config"]["workload"] += f" (only {layers} blocks fit in free device memory)"
+        line["config"]["layers"] = layers
+    if world == 1 and not args.no_cpu_baseline:
+        seconds, times = time_cpu_layer(runs=10, warmup=2)
+        cores = os.cpu_count() or 1
+        line["cpu_baseline"] = {
+            "value": 1.0 / (seconds * layers), "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"median of 10 forwards of one block (config[0]) through the CPU oracle, {cores} threads; "
+                      f"scaled to {layers} blocks per token", "block_seconds": seconds}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=50)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--layers", type=int, default=40)
+    parser.add_argument("--no-graph", action="store_true", help="eager launches instead of graph replay")
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    args = parser.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,152 @@
+/* C ABI of the B200 (sm_100a) NVFP4 routed-expert path.
+ *
+ * Every entry point takes raw device pointers, plain integers and the CUDA stream to
+ * launch on, allocates nothing, never synchronises, and returns 0 on success or a
+ * negative code (ink_last_error() gives the message of the calling thread's last
+ * failure). All are safe to call during CUDA-graph stream capture. "Reference" below
+ * is Sourish07/Inkling-vs-Quad-RTX-3090s; each declaration names the interface it
+ * stands in for.
+ *
+ * Conventions: activations and router weights are BF16 (passed as void*), expert
+ * indices int64, pointer tables int64 device addresses laid out [expert][bank] with
+ * the bank order of kernels/grouped_experts.py:9-22
+ *   NVFP4: gate_up_proj, gate_up_proj_scale, gate_up_proj_scale2,
+ *          down_proj,    down_proj_scale,    down_proj_scale2        (stride 6)
+ * A zero first entry means "expert not on this rank / inactive": its routes are
+ * skipped. NVFP4 banks: codes uint8 [rows, K/2] (two E2M1 codes per byte, low nibble
+ * = even column), scales E4M3 bytes [rows, K/16], scale2 one FP32 read through its
+ * pointer. gate_up rows interleave gate (even) and up (odd).
+ */
+#ifndef INKLING_B200_H_
+#define INKLING_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* ink_stream_t; /* == cudaStream_t */
+
+/* Message of this thread's most recent failing call ("" if none). */
+const char* ink_last_error(void);
+
+/* Library/ABI version, bumped when a signature changes. */
+int ink_abi_version(void);
+
+/* ---------------------------------------------------------------- router ------
+ * Replaces MyInklingTopkRouter.forward (my_inkling/model.py:311-350): BF16 logits =
+ * x . W^T, score = bf16(sigmoid(logit)) + bias (FP32), top_k largest scores (ties:
+ * lower expert id wins; emitted in descending score order), weights =
+ * softmax(logsigmoid(selected + shared logits)) * route_scale * global_scale with the
+ * BF16 rounding after every step that the reference's BF16 tensors impose.
+ *
+ *  x             BF16 [tokens, hidden]
+ *  weight        BF16 [n_routed + n_shared, hidden]
+ *  bias          FP32 [n_routed]
+ *  global_scale  BF16 [1]
+ *  routed_logits BF16 [tokens, n_routed] or NULL
+ *  topk_weights  BF16 [tokens, top_k]; topk_indices int64 [tokens, top_k]
+ *  shared_gammas BF16 [tokens, n_shared]
+ *  workspace     ink_router_workspace_bytes(tokens, n_routed + n_shared) bytes,
+ *                zero-filled once before first use (the kernel leaves it reusable)
+ * Constraints: hidden % 8 == 0, n_routed % 32 == 0, n_routed <= 512, top_k <= 32,
+ * top_k + n_shared <= 32.
+ */
+size_t ink_router_workspace_bytes(int tokens, int n_experts_total);
+int ink_router_forward(const void* x, const void* weight, const float* bias, const void* global_scale,
+                       float route_scale, int tokens, int hidden, int n_routed, int n_shared, int top_k,
+                       void* routed_logits, void* topk_weights, int64_t* topk_indices,
+                       void* shared_gammas, void* workspace, size_t workspace_bytes,
+                       ink_stream_t stream);
+
+/* Router and expert plan in ONE launch (decode: tokens * top_k <= 512 routes); the
+ * plan arguments are those of ink_expert_plan below. */
+int ink_router_plan_forward(const void* x, const void* weight, const float* bias, const void* global_scale,
+                            float route_scale, int tokens, int hidden, int n_routed, int n_shared, int top_k,
+                            void* routed_logits, void* topk_weights, int64_t* topk_indices,
+                            void* shared_gammas, void* workspace, size_t workspace_bytes,
+                            const int64_t* sources, int64_t* pointers, int32_t* experts, int32_t* counts,
+                            int32_t* rows, int start, int local, int stride, int capacity,
+                            ink_stream_t stream);
+
+/* ------------------------------------------------------------------ plan ------
+ * Replaces the Triton kernel expert_plan (kernels/expert_planner.py:11-113) for a
+ * placement in which every expert is resident (its LRU/slot outputs do not exist):
+ *  counts per expert START+e, active experts compacted in ascending id into
+ *  experts[] (-1 after) / counts[] (0 after), rows[g, :counts[g]] = ascending route
+ *  numbers (route = token * top_k + choice), pointers[(start+e)*stride + b] =
+ *  sources[e*stride + b] if the expert has routes else 0.
+ * rows beyond counts[g] are left untouched, as in the reference.
+ */
+int ink_expert_plan(const int64_t* indices, const int64_t* sources, int64_t* pointers, int32_t* experts,
+                    int32_t* counts, int32_t* rows, int start, int local, int stride, int routes,
+                    int capacity, ink_stream_t stream);
+
+/* ---------------------------------------------------------- decode GEMV ------
+ * Replaces routed_decode (kernels/routed_decode.py:25-80) and its two CUDA kernels
+ * gate_up / down_reduce (kernels/routed_decode.cu:137-173, :178-219):
+ *   activated[route] = bf16(silu(gate) * up)        gate/up = scale2 * (W_gate_up . x)
+ *   output[token]    = sum over choices of fp32(bf16(bf16(scale2 * (W_down . activated[route])) * w))
+ * NVFP4 banks (quantized = 1) only in this build. output is fully overwritten;
+ * activated is scratch [tokens*top_k, intermediate].
+ *  status: optional int32 device word; bit 0 is set when a route names an expert
+ *          outside [0, max_expert] (the reference skips such routes silently).
+ * Constraints: hidden and intermediate powers of two between 64 and 4096; top_k <= 30;
+ * all buffers 16-byte aligned. An E4M3 scale byte 0x7F/0xFF decodes to NaN here (the
+ * reference's table gives +-480); valid NVFP4 scales never use those codes.
+ */
+int ink_routed_decode(const void* x, const int64_t* indices, const void* weights, const int64_t* pointers,
+                      void* activated, float* output, int tokens, int top_k, int hidden, int intermediate,
+                      int max_expert, int quantized, int32_t* status, ink_stream_t stream);
+
+/* Whole MoE layer at decode in two launches: the routed NVFP4 experts (as above) PLUS
+ * the shared BF16 experts of MyInklingSharedExperts.forward (my_inkling/model.py:
+ * 192-226; TP shard of my_inkling/tp_plan.py:128-146): per shared expert e
+ *   act_e = bf16(bf16(bf16(silu(bf16 gate)) * bf16 up) * gamma_e),  down_e = bf16(W_down_e . act_e)
+ * and output[token] = routed sum + sum_e fp32(down_e), FP32, fully overwritten: the
+ * per-rank partial that one all-reduce then sums.
+ *  shared_gate/up BF16 [n_shared, intermediate, hidden]; shared_down BF16 [n_shared, hidden, intermediate]
+ *  gammas BF16 [tokens, n_shared]; shared_activated scratch BF16 [tokens*n_shared, intermediate]
+ */
+int ink_moe_decode(const void* x, const int64_t* indices, const void* weights, const int64_t* pointers,
+                   void* activated, const void* shared_gate, const void* shared_up, const void* shared_down,
+                   const void* gammas, void* shared_activated, float* output, int tokens, int top_k,
+                   int n_shared, int hidden, int intermediate, int max_expert, int32_t* status,
+                   ink_stream_t stream);
+
+/* The two launches of ink_moe_decode on their own (same arguments): the gate/up half
+ * writes activated / shared_activated, the down half reads them and writes output.
+ * Lets a caller place other work between the halves, or time them apart. */
+int ink_moe_gate_up(const void* x, const int64_t* indices, const void* weights, const int64_t* pointers,
+                    void* activated, const void* shared_gate, const void* shared_up, const void* shared_down,
+                    const void* gammas, void* shared_activated, float* output, int tokens, int top_k,
+                    int n_shared, int hidden, int intermediate, int max_expert, int32_t* status,
+                    ink_stream_t stream);
+int ink_moe_down(const void* x, const int64_t* indices, const void* weights, const int64_t* pointers,
+                 void* activated, const void* shared_gate, const void* shared_up, const void* shared_down,
+                 const void* gammas, void* shared_activated, float* output, int tokens, int top_k,
+                 int n_shared, int hidden, int intermediate, int max_expert, int32_t* status,
+                 ink_stream_t stream);
+
+/* ------------------------------------------------------------ layer glue ------
+ * What sits either side of the MoE block in MyInklingDecoderLayer.forward
+ * (my_inkling/model.py:672-675), reduced to its arithmetic skeleton for a stack of MoE
+ * layers: the block's FP32 output is cast to BF16 and added to the residual stream
+ * (BF16 add), and the sum is RMS-normalised for the next block exactly as the
+ * reference's _rms_norm does (kernels/decode.py:36-43: FP32 reduction, the normalised
+ * value rounded to BF16 BEFORE it is multiplied by the weight).
+ *  partial   FP32 [tokens, hidden] (the all-reduced MoE output)
+ *  residual  BF16 [tokens, hidden], updated in place to residual + bf16(partial)
+ *  weight    BF16 [hidden]
+ *  normed    BF16 [tokens, hidden]
+ * Constraint: hidden % 8 == 0, hidden <= 16384.
+ */
+int ink_add_rmsnorm(const float* partial, void* residual, const void* weight, float eps, void* normed,
+                    int tokens, int hidden, ink_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* INKLING_B200_H_ */

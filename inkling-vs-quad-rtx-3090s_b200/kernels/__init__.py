@@ -1,0 +1,18 @@
+"""Drop-in counterpart of the reference's `kernels` package for the NVFP4
+routed-expert path: same names, same call signatures, sm_100a library underneath."""
+from .expert_planner import expert_copy, expert_plan
+from .grouped_experts import expert_bank_names
+from .routed_decode import add_rmsnorm, moe_decode, routed_decode
+from .router import router_forward, router_plan_forward, router_workspace
+
+__all__ = [
+    "add_rmsnorm",
+    "expert_bank_names",
+    "expert_copy",
+    "expert_plan",
+    "moe_decode",
+    "routed_decode",
+    "router_forward",
+    "router_plan_forward",
+    "router_workspace",
+]
