@@ -266,25 +266,48 @@ def run_ours(args) -> None:
         e2e_ms = float(t.item())
     finite = bool(torch.isfinite(host_out.float()).all())
 
-    # ---- per-kernel durations for the roofline: one launch per block (distinct weights,
-    # so nothing is L2-warm), events on the launching stream
-    def time_half(half: str, rounds: int = 3) -> float:
-        best = []
+    # ---- per-kernel durations for the roofline: the same kernel launched once per block of
+    # the stack (distinct weights each time, so nothing is L2-warm), captured into a CUDA
+    # graph so that the host's launch cost is not in the number, timed with events on the
+    # stream that replays it
+    def time_graph(fn, rounds: int = 5) -> float:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for layer in stack.layers:
+                fn(layer)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for layer in stack.layers:
+                fn(layer)
+        times = []
         for _ in range(rounds + 1):
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
-            for layer in stack.layers:
-                ex = layer.experts
-                ib.kernels.moe_decode(stack.normed[:1], layer.topk_indices[:1], layer.topk_weights[:1], ex.pointers,
-                                      ex.activated, layer.shared_gate, layer.shared_up, layer.shared_down,
-                                      layer.gammas[:1], layer.shared_activated, layer.partial[:1], ex.max_expert,
-                                      status=ex.status, half=half)
+            graph.replay()
             b.record()
             torch.cuda.synchronize()
-            best.append(a.elapsed_time(b) / len(stack.layers))
-        return sum(best[1:]) / rounds   # first round is warm-up
+            times.append(a.elapsed_time(b) / len(stack.layers))
+        return sum(times[1:]) / rounds   # first replay is warm-up
 
-    kernel_ms = {half: time_half(half) for half in ("gate_up", "down")}
+    def half(which):
+        def run(layer):
+            ex = layer.experts
+            ib.kernels.moe_decode(stack.normed[:1], layer.topk_indices[:1], layer.topk_weights[:1], ex.pointers,
+                                  ex.activated, layer.shared_gate, layer.shared_up, layer.shared_down,
+                                  layer.gammas[:1], layer.shared_activated, layer.partial[:1], ex.max_expert,
+                                  status=ex.status, half=which)
+        return run
+
+    kernel_ms = {
+        "gate_up": time_graph(half("gate_up")),
+        "down": time_graph(half("down")),
+        "router_plan": time_graph(lambda layer: layer.route(stack.normed[:1])),
+        "add_rmsnorm": time_graph(lambda layer: ib.kernels.add_rmsnorm(
+            layer.partial[:1], stack.residual[:1], stack.norm_weight, stack.eps, stack.normed[:1])),
+    }
     barrier()
     if rank != 0:
         if world > 1:
@@ -314,6 +337,7 @@ def run_ours(args) -> None:
         "kernels": {
             "down_kernel": {"launch_ms": kernel_ms["down"], "algorithmic_bytes": bytes_["down"],
                             "achieved_gbs": bytes_["down"] / (kernel_ms["down"] * 1e-3) / 1e9},
+            "router_plan_launch_ms": kernel_ms["router_plan"], "add_rmsnorm_launch_ms": kernel_ms["add_rmsnorm"],
             "layer_bytes_per_rank": bytes_["total"],
             "stack_achieved_gbs": bytes_["total"] * layers * tok_s / 1e9,
             "stack_frac_of_peak": bytes_["total"] * layers * tok_s / 1e9 / peaks["hbm_gbs"],

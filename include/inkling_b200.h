@@ -51,8 +51,7 @@ int ink_abi_version(void);
  *  shared_gammas BF16 [tokens, n_shared]
  *  workspace     ink_router_workspace_bytes(tokens, n_routed + n_shared) bytes,
  *                zero-filled once before first use (the kernel leaves it reusable)
- * Constraints: hidden % 8 == 0, n_routed % 32 == 0, n_routed <= 512, top_k <= 32,
- * top_k + n_shared <= 32.
+ * Constraints: hidden % 8 == 0, top_k <= n_routed <= 512, top_k + n_shared <= 32.
  */
 size_t ink_router_workspace_bytes(int tokens, int n_experts_total);
 int ink_router_forward(const void* x, const void* weight, const float* bias, const void* global_scale,

@@ -16,7 +16,7 @@ from pathlib import Path
 CSRC = Path(__file__).resolve().parent
 PACKAGE = CSRC.parent
 LIBRARY = PACKAGE / "libinkling_b200.so"
-SOURCES = ("router_plan.cu", "routed_decode.cu", "glue.cu")
+SOURCES = ("router_plan.cu", "routed_decode.cu", "stream_decode.cu", "glue.cu")
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xptxas=-v",
@@ -34,7 +34,7 @@ def needs_build() -> bool:
     if not LIBRARY.exists():
         return True
     stamp = LIBRARY.stat().st_mtime
-    inputs = [CSRC / s for s in SOURCES] + list(CSRC.glob("*.cuh")) + [PACKAGE.parent / "include" / "inkling_b200.h"]
+    inputs = [CSRC / s for s in SOURCES] + list(CSRC.glob("*.cuh")) + [Path(__file__)] + [PACKAGE.parent / "include" / "inkling_b200.h"]
     return any(p.stat().st_mtime > stamp for p in inputs)
 
 

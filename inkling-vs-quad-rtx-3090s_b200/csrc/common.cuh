@@ -43,6 +43,19 @@ enum DeviceFlag : int {
     }                                                                       \
   } while (0)
 
+// Every kernel of the library asks for the largest shared-memory carve-out, so that the
+// SMs are not re-partitioned between L1 and shared memory from one launch to the next
+// (the streaming kernels need almost all of it).
+#define INK_PREFER_MAX_SMEM(kernel)                                                             \
+  do {                                                                                          \
+    static bool done_ = false;                                                                  \
+    if (!done_) {                                                                               \
+      cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,              \
+                           (int)cudaSharedmemCarveoutMaxShared);                                \
+      done_ = true;                                                                             \
+    }                                                                                           \
+  } while (0)
+
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // ------------------------------------------------------------------- BF16 <-> FP32

@@ -79,6 +79,7 @@ extern "C" int ink_add_rmsnorm(const float* partial, void* residual, const void*
   INK_REQUIRE(aligned16(partial) && aligned16(residual) && aligned16(weight) && aligned16(normed), kMisaligned,
               "add_rmsnorm: buffers must be 16-byte aligned");
   if (tokens == 0) return kOk;
+  INK_PREFER_MAX_SMEM(add_rmsnorm_kernel);
   add_rmsnorm_kernel<<<tokens, kNormThreads, 0, (cudaStream_t)stream>>>(
       partial, (uint16_t*)residual, (const uint16_t*)weight, eps, (uint16_t*)normed, hidden);
   INK_CHECK_LAUNCH("add_rmsnorm");

@@ -7,27 +7,9 @@
 //   down_kernel    : output[token]    = sum_routes bf16(bf16(down) * w) + sum_shared bf16(down)
 #include "../../include/inkling_b200.h"
 #include "common.cuh"
+#include "decode_args.cuh"
 
 namespace ink {
-
-constexpr int kBank = 6;            // pointer-table entries per NVFP4 expert
-constexpr int kBatchLoads = 8;      // 16-byte weight loads a lane keeps in flight
-
-struct DecodeArgs {
-  const uint16_t* x;                // [tokens, hidden] BF16
-  const int64_t* indices;           // [tokens * top_k]
-  const uint16_t* weights;          // [tokens * top_k] BF16
-  const int64_t* pointers;          // [(max_expert + 1) * 6]
-  uint16_t* activated;              // [tokens * top_k, intermediate] BF16
-  const uint16_t* shared_gate;      // [n_shared, intermediate, hidden] BF16
-  const uint16_t* shared_up;
-  const uint16_t* shared_down;      // [n_shared, hidden, intermediate] BF16
-  const uint16_t* gammas;           // [tokens, n_shared] BF16
-  uint16_t* shared_activated;       // [tokens * n_shared, intermediate] BF16
-  float* output;                    // [tokens, hidden] FP32
-  int tokens, top_k, n_shared, hidden, intermediate, max_expert;
-  int32_t* status;
-};
 
 // Geometry of one NVFP4 row of K columns seen by a warp: a row is K/32 chunks of 16
 // bytes (32 weights, two scale bytes); LPR lanes share a row, each lane owns CPL chunks,
@@ -374,7 +356,7 @@ __global__ void __launch_bounds__(kDownThreads) down_kernel(DecodeArgs a, int ti
       }
     }
   }
-  if (lane < T::ROWS_PER_WARP) s_total[warp][lane] = 0.f;
+  for (int i = lane; i < T::ROWS_PER_WARP; i += 32) s_total[warp][i] = 0.f;
   __syncthreads();
   const int warp_row0 = tile * T::ROWS + warp * T::ROWS_PER_WARP;
   const int sl = lane % M::LPR, rp = lane / M::LPR;
@@ -420,8 +402,8 @@ __global__ void __launch_bounds__(kDownThreads) down_kernel(DecodeArgs a, int ti
     __syncwarp();
   }
   __syncwarp();
-  if (lane < T::ROWS_PER_WARP && warp_row0 + lane < d)
-    a.output[(size_t)token * d + warp_row0 + lane] = s_total[warp][lane];
+  for (int i = lane; i < T::ROWS_PER_WARP; i += 32)
+    if (warp_row0 + i < d) a.output[(size_t)token * d + warp_row0 + i] = s_total[warp][i];
 }
 
 // ---------------------------------------------------------------- launchers
@@ -432,6 +414,7 @@ static int launch_gate_up(const DecodeArgs& a, cudaStream_t stream) {
   const int s_tiles = (a.intermediate + GateUpTile<K>::S_PAIRS - 1) / GateUpTile<K>::S_PAIRS;
   const long long blocks = (long long)routes * q_tiles + (long long)a.tokens * a.n_shared * s_tiles;
   if (blocks == 0) return kOk;
+  INK_PREFER_MAX_SMEM(gate_up_kernel<K>);
   gate_up_kernel<K><<<(unsigned)blocks, kGateUpThreads, 0, stream>>>(a, q_tiles, s_tiles);
   INK_CHECK_LAUNCH("gate_up");
   return kOk;
@@ -448,6 +431,7 @@ static int launch_down(const DecodeArgs& a, cudaStream_t stream) {
                 cudaGetErrorString(e));
     configured = smem;
   }
+  INK_PREFER_MAX_SMEM(down_kernel<K>);
   down_kernel<K><<<(unsigned)(a.tokens * tiles), kDownThreads, smem, stream>>>(a, tiles);
   INK_CHECK_LAUNCH("down");
   return kOk;
@@ -479,6 +463,7 @@ static int dispatch_down(const DecodeArgs& a, cudaStream_t stream) {
 static int check_decode(const DecodeArgs& a, bool with_shared) {
   INK_REQUIRE(a.tokens >= 0 && a.top_k >= 1 && a.top_k <= 30 && a.max_expert >= 0, kBadArgument,
               "decode: tokens=%d top_k=%d max_expert=%d", a.tokens, a.top_k, a.max_expert);
+  if (a.tokens == 0) return kOk;  // nothing to read or write: pointers may be null
   INK_REQUIRE(a.x && a.indices && a.weights && a.pointers && a.activated && a.output, kBadArgument,
               "decode: null pointer argument");
   INK_REQUIRE(aligned16(a.x) && aligned16(a.indices) && aligned16(a.weights) && aligned16(a.activated) &&
@@ -494,6 +479,12 @@ static int check_decode(const DecodeArgs& a, bool with_shared) {
   }
   return kOk;
 }
+
+// streaming kernels for the production widths (stream_decode.cu)
+bool stream_gate_up_supported(const DecodeArgs& a);
+bool stream_down_supported(const DecodeArgs& a);
+int dispatch_gate_up_stream(const DecodeArgs& a, cudaStream_t stream);
+int dispatch_down_stream(const DecodeArgs& a, cudaStream_t stream);
 
 }  // namespace ink
 
@@ -539,6 +530,7 @@ extern "C" int ink_moe_gate_up(INK_MOE_PARAMS) {
   DecodeArgs a = make_decode_args(INK_MOE_ARGS);
   if (int rc = check_decode(a, true)) return rc;
   if (tokens == 0) return kOk;
+  if (stream_gate_up_supported(a)) return dispatch_gate_up_stream(a, (cudaStream_t)stream);
   return dispatch_gate_up(a, (cudaStream_t)stream);
 }
 
@@ -546,6 +538,7 @@ extern "C" int ink_moe_down(INK_MOE_PARAMS) {
   DecodeArgs a = make_decode_args(INK_MOE_ARGS);
   if (int rc = check_decode(a, true)) return rc;
   if (tokens == 0) return kOk;
+  if (stream_down_supported(a)) return dispatch_down_stream(a, (cudaStream_t)stream);
   return dispatch_down(a, (cudaStream_t)stream);
 }
 

@@ -34,6 +34,7 @@ struct RouterArgs {
   int64_t* topk_indices;
   uint16_t* shared_gammas;
   float* logits;           // workspace: [tokens, n_routed + n_shared] BF16-rounded logits as FP32
+  float* scores;           // workspace: [tokens, n_routed] selection scores
   unsigned int* counter;   // workspace: blocks done
 };
 
@@ -48,34 +49,32 @@ struct PlanArgs {
 };
 
 // ------------------------------------------------------------------ one token
-// Executed by one warp. Scores live in registers: lane l owns experts l, l+32, ...
-__device__ void router_finish_token(const RouterArgs& a, int token) {
+// Executed by one warp. `score` is this warp's shared-memory scratch of n_routed floats:
+// score[e] = bf16(sigmoid(logit_e)) + bias_e, computed by the blocks that produced the
+// logits. Small loops on purpose: this code runs once, on one warp, straight out of a
+// cold instruction cache.
+__device__ void router_finish_token(const RouterArgs& a, int token, float* score, int* ids_out) {
   const int lane = threadIdx.x & 31;
   const int total = a.n_routed + a.n_shared;
   const float* logit = a.logits + (size_t)token * total;
-  const int per_lane = a.n_routed / 32;
-  float score[kMaxScoresPerLane];
-#pragma unroll
-  for (int j = 0; j < kMaxScoresPerLane; ++j) {
-    score[j] = -INFINITY;
-    if (j < per_lane) {
-      const int e = j * 32 + lane;
-      const float l = __ldcg(logit + e);
-      if (a.routed_logits) a.routed_logits[(size_t)token * a.n_routed + e] = (uint16_t)f32_to_bf16_bits(l);
-      // BF16 sigmoid, then FP32 add of the FP32 bias
-      score[j] = round_bf16(1.f / (1.f + expf(-l))) + a.bias[e];
-    }
+  const float* scores = a.scores + (size_t)token * a.n_routed;
+  for (int e = lane; e < a.n_routed; e += 32) {
+    score[e] = __ldcg(scores + e);
+    if (a.routed_logits) a.routed_logits[(size_t)token * a.n_routed + e] = (uint16_t)f32_to_bf16_bits(__ldcg(logit + e));
   }
+  __syncwarp();
   // top-k by repeated arg-max; ties go to the lower expert id
-  int my_choice = -1;  // lane r < top_k ends up holding the r-th choice
+  int my_choice = 0;  // lane r < top_k ends up holding the r-th choice
+#pragma unroll 1
   for (int r = 0; r < a.top_k; ++r) {
     float best = -INFINITY;
     int best_e = 0x7fffffff;
-#pragma unroll
-    for (int j = 0; j < kMaxScoresPerLane; ++j) {
-      if (j < per_lane && (score[j] > best || (score[j] == best && j * 32 + lane < best_e && score[j] > -INFINITY))) {
-        best = score[j];
-        best_e = j * 32 + lane;
+#pragma unroll 1
+    for (int e = lane; e < a.n_routed; e += 32) {
+      const float v = score[e];
+      if (v > best) {  // ascending e within a lane: a later equal value never replaces
+        best = v;
+        best_e = e;
       }
     }
 #pragma unroll
@@ -88,12 +87,9 @@ __device__ void router_finish_token(const RouterArgs& a, int token) {
       }
     }
     if (best_e == 0x7fffffff) best_e = r;  // every score is -inf/NaN: fall back to a valid id
-    if ((best_e & 31) == lane) {
-#pragma unroll
-      for (int j = 0; j < kMaxScoresPerLane; ++j)
-        if (j == (best_e >> 5)) score[j] = -INFINITY;
-    }
+    if (lane == 0) score[best_e] = -INFINITY;
     if (lane == r) my_choice = best_e;
+    __syncwarp();
   }
   // weights over the top_k selected logits followed by the shared logits
   const int n = a.top_k + a.n_shared;
@@ -102,23 +98,24 @@ __device__ void router_finish_token(const RouterArgs& a, int token) {
   if (lane < a.top_k) l = __ldcg(logit + my_choice);
   else if (live) l = __ldcg(logit + a.n_routed + (lane - a.top_k));
   // logsigmoid = min(0, x) - log1p(exp(-|x|)), result rounded to BF16
-  const float lp = live ? round_bf16(fminf(0.f, l) - log1pf(expf(-fabsf(l)))) : -INFINITY;
+  const float lp = live ? round_bf16(fminf(0.f, l) - log1pf(__expf(-fabsf(l)))) : -INFINITY;
   float m = lp;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
   if (fabsf(m) == INFINITY) m = 0.f;
   // logsumexp as torch composes it: exp(bf16(lp - max)) rounded, FP32 sum rounded, log rounded, + max rounded
-  const float ex = live ? round_bf16(expf(round_bf16(lp - m))) : 0.f;
+  const float ex = live ? round_bf16(__expf(round_bf16(lp - m))) : 0.f;
   float s = ex;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-  const float lse = round_bf16(round_bf16(logf(round_bf16(s))) + m);
-  float w = round_bf16(expf(round_bf16(lp - lse)));
+  const float lse = round_bf16(round_bf16(__logf(round_bf16(s))) + m);
+  float w = round_bf16(__expf(round_bf16(lp - lse)));
   w = round_bf16(w * a.route_scale);
   w = round_bf16(w * bf16_to_f32(a.global_scale[0]));
   if (lane < a.top_k) {
     a.topk_indices[(size_t)token * a.top_k + lane] = my_choice;
     a.topk_weights[(size_t)token * a.top_k + lane] = (uint16_t)f32_to_bf16_bits(w);
+    if (ids_out) ids_out[token * a.top_k + lane] = my_choice;
   } else if (live) {
     a.shared_gammas[(size_t)token * a.n_shared + (lane - a.top_k)] = (uint16_t)f32_to_bf16_bits(w);
   }
@@ -126,10 +123,10 @@ __device__ void router_finish_token(const RouterArgs& a, int token) {
 
 // ------------------------------------------------------------- single-block plan
 // routes <= kPlanSmallRoutes. Whole block; `ids` is shared memory for the routes.
-__device__ void plan_small(const PlanArgs& p, int* ids, int* warp_totals) {
+__device__ void plan_small(const PlanArgs& p, int* ids, int* warp_totals, bool ids_loaded) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, warps = blockDim.x >> 5;
   for (int r = tid; r < p.routes; r += blockDim.x) {
-    const int64_t id = p.indices[r];
+    const int64_t id = ids_loaded ? (int64_t)ids[r] : p.indices[r];
     ids[r] = (id >= p.start && id < (int64_t)p.start + p.local) ? (int)(id - p.start) : -1;
   }
   __syncthreads();
@@ -180,6 +177,7 @@ __global__ void __launch_bounds__(kFinishThreads) router_kernel(RouterArgs a, Pl
   __shared__ int s_ids[kPlanSmallRoutes];
   __shared__ int s_warp_totals[32];
   __shared__ float s_part[kRowsPerBlock][kWarpsPerRow][TG];
+  __shared__ float s_score[kFinishThreads / 32][32 * kMaxScoresPerLane];
   __shared__ bool s_last;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   const int total = a.n_routed + a.n_shared;
@@ -226,7 +224,11 @@ __global__ void __launch_bounds__(kFinishThreads) router_kernel(RouterArgs a, Pl
         float s = 0.f;
 #pragma unroll
         for (int w = 0; w < kWarpsPerRow; ++w) s += s_part[r][w][t];
-        a.logits[(size_t)(t0 + t) * total + out_row] = round_bf16(s);
+        const float l = round_bf16(s);
+        a.logits[(size_t)(t0 + t) * total + out_row] = l;
+        // BF16 sigmoid, then FP32 add of the FP32 bias: the value the top-k compares
+        if (out_row < a.n_routed)
+          a.scores[(size_t)(t0 + t) * a.n_routed + out_row] = round_bf16(1.f / (1.f + __expf(-l))) + a.bias[out_row];
       }
     }
     __syncthreads();
@@ -241,10 +243,11 @@ __global__ void __launch_bounds__(kFinishThreads) router_kernel(RouterArgs a, Pl
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  for (int token = warp; token < a.tokens; token += warps) router_finish_token(a, token);
+  for (int token = warp; token < a.tokens; token += warps)
+    router_finish_token(a, token, s_score[warp], kFusePlan ? s_ids : nullptr);
   if (kFusePlan) {
     __syncthreads();
-    plan_small(p, s_ids, s_warp_totals);
+    plan_small(p, s_ids, s_warp_totals, true);
   }
   if (threadIdx.x == 0) *a.counter = 0u;  // leave the workspace ready for the next call
 }
@@ -252,7 +255,7 @@ __global__ void __launch_bounds__(kFinishThreads) router_kernel(RouterArgs a, Pl
 __global__ void __launch_bounds__(kFinishThreads) plan_small_kernel(PlanArgs p) {
   __shared__ int s_ids[kPlanSmallRoutes];
   __shared__ int s_warp_totals[32];
-  plan_small(p, s_ids, s_warp_totals);
+  plan_small(p, s_ids, s_warp_totals, false);
 }
 
 // ------------------------------------------------------------- plan, any size
@@ -320,8 +323,8 @@ __global__ void __launch_bounds__(256) plan_rows_kernel(PlanArgs p) {
 static int check_router(const RouterArgs& a, size_t workspace_bytes) {
   INK_REQUIRE(a.tokens >= 0 && a.hidden > 0, kBadArgument, "router: tokens=%d hidden=%d", a.tokens, a.hidden);
   INK_REQUIRE(a.hidden % 8 == 0, kUnsupportedShape, "router: hidden=%d must be a multiple of 8", a.hidden);
-  INK_REQUIRE(a.n_routed % 32 == 0 && a.n_routed > 0 && a.n_routed <= 32 * kMaxScoresPerLane, kUnsupportedShape,
-              "router: n_routed=%d must be a multiple of 32 and at most %d", a.n_routed, 32 * kMaxScoresPerLane);
+  INK_REQUIRE(a.n_routed > 0 && a.n_routed <= 32 * kMaxScoresPerLane, kUnsupportedShape,
+              "router: n_routed=%d must be between 1 and %d", a.n_routed, 32 * kMaxScoresPerLane);
   INK_REQUIRE(a.top_k >= 1 && a.top_k <= 32 && a.top_k <= a.n_routed && a.n_shared >= 0 && a.top_k + a.n_shared <= 32,
               kUnsupportedShape, "router: top_k=%d n_shared=%d unsupported", a.top_k, a.n_shared);
   INK_REQUIRE(a.x && a.weight && a.bias && a.global_scale && a.topk_weights && a.topk_indices &&
@@ -351,8 +354,8 @@ extern "C" const char* ink_last_error(void) { return g_error; }
 extern "C" int ink_abi_version(void) { return 1; }
 
 extern "C" size_t ink_router_workspace_bytes(int tokens, int n_experts_total) {
-  // 256 bytes of counters, then the FP32 logits
-  return 256 + sizeof(float) * (size_t)(tokens > 0 ? tokens : 0) * (size_t)n_experts_total;
+  // 256 bytes of counters, then the FP32 logits and the FP32 selection scores
+  return 256 + 2 * sizeof(float) * (size_t)(tokens > 0 ? tokens : 0) * (size_t)n_experts_total;
 }
 
 static RouterArgs make_router_args(const void* x, const void* weight, const float* bias, const void* global_scale,
@@ -376,6 +379,7 @@ static RouterArgs make_router_args(const void* x, const void* weight, const floa
   a.shared_gammas = (uint16_t*)shared_gammas;
   a.counter = (unsigned int*)workspace;
   a.logits = workspace ? (float*)((char*)workspace + 256) : nullptr;
+  a.scores = a.logits ? a.logits + (size_t)(tokens > 0 ? tokens : 0) * (size_t)(n_routed + n_shared) : nullptr;
   return a;
 }
 
@@ -389,6 +393,8 @@ extern "C" int ink_router_forward(const void* x, const void* weight, const float
   if (int rc = check_router(a, workspace_bytes)) return rc;
   if (tokens == 0) return kOk;
   const int blocks = (n_routed + n_shared + kRowsPerBlock - 1) / kRowsPerBlock;
+  INK_PREFER_MAX_SMEM((router_kernel<false, 1>));
+  INK_PREFER_MAX_SMEM((router_kernel<false, kTokenGroup>));
   if (tokens == 1)
     router_kernel<false, 1><<<blocks, kFinishThreads, 0, (cudaStream_t)stream>>>(a, PlanArgs{});
   else
@@ -415,6 +421,8 @@ extern "C" int ink_router_plan_forward(const void* x, const void* weight, const 
   INK_REQUIRE(capacity >= p.routes || capacity >= tokens, kBadArgument, "router_plan: capacity=%d too small", capacity);
   if (tokens == 0) return kOk;
   const int blocks = (n_routed + n_shared + kRowsPerBlock - 1) / kRowsPerBlock;
+  INK_PREFER_MAX_SMEM((router_kernel<true, 1>));
+  INK_PREFER_MAX_SMEM((router_kernel<true, kTokenGroup>));
   if (tokens == 1)
     router_kernel<true, 1><<<blocks, kFinishThreads, 0, (cudaStream_t)stream>>>(a, p);
   else
@@ -429,12 +437,15 @@ extern "C" int ink_expert_plan(const int64_t* indices, const int64_t* sources, i
   PlanArgs p{indices, sources, pointers, experts, counts, rows, start, local, stride, routes, capacity};
   if (int rc = check_plan(p)) return rc;
   if (routes <= kPlanSmallRoutes) {
+    INK_PREFER_MAX_SMEM(plan_small_kernel);
     plan_small_kernel<<<1, kFinishThreads, 0, (cudaStream_t)stream>>>(p);
     INK_CHECK_LAUNCH("ink_expert_plan");
     return kOk;
   }
   // large plans borrow counts[] as the histogram: pass 1 rewrites it in compacted order
   // only after every histogram entry has been read into a register.
+  INK_PREFER_MAX_SMEM(plan_count_kernel);
+  INK_PREFER_MAX_SMEM(plan_rows_kernel);
   plan_count_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(p, p.counts);
   INK_CHECK_LAUNCH("ink_expert_plan(count)");
   const int warps = 8;

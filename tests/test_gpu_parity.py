@@ -380,7 +380,7 @@ def test_baseline_shape_properties(ib, device, baseline_layer):
     full_table = ex.sources.reshape(-1).clone()
     base = run(x, idx, w, full_table)
     # (3)
-    singles = torch.cat([run(x[i:i + 1], idx[i:i + 1], w[i:i + 1], full_table) for i in range(8)])
+    singles = torch.cat([run(x[i:i + 1], idx[i:i + 1].clone(), w[i:i + 1].clone(), full_table) for i in range(8)])
     assert torch.equal(base, singles)
     # (2)
     assert torch.equal(run(x, idx, (w.float() * 2).to(BF16), full_table), base * 2)
@@ -390,6 +390,6 @@ def test_baseline_shape_properties(ib, device, baseline_layer):
         table = torch.zeros_like(full_table).view(-1, 6)
         e = int(idx[0, choice])
         table[e] = full_table.view(-1, 6)[e]
-        total += run(x[:1], idx[:1], w[:1], table.reshape(-1))[0]
+        total += run(x[:1], idx[:1].clone(), w[:1].clone(), table.reshape(-1))[0]
     assert torch.equal(total, base[0])
     torch.cuda.synchronize()
