@@ -145,6 +145,44 @@ int ink_moe_down(const void* x, const int64_t* indices, const void* weights, con
 int ink_add_rmsnorm(const float* partial, void* residual, const void* weight, float eps, void* normed,
                     int tokens, int hidden, ink_stream_t stream);
 
+/* ------------------------------------------------- whole stack, one launch ------
+ * One decode token through n_layers MoE blocks in ONE persistent cooperative kernel:
+ * per block the router (as ink_router_forward), the expert plan (resolved to bank
+ * addresses on the device), the routed and shared experts (as ink_moe_decode), and --
+ * with glue = 1 -- the residual add and RMS norm that ink_add_rmsnorm performs between
+ * blocks. It replaces, for one token, the launches MyInklingMoE.forward issues per block
+ * (my_inkling/model.py:361-374 through my_inkling/offloaded_experts.py:298-314).
+ *
+ *  layers       device array of n_layers descriptors, ink_moe_stack_layer_bytes() each:
+ *               struct { const void *router_weight; const float *router_bias;
+ *                        const void *global_scale; const int64_t *sources;    (sources: [experts][6])
+ *                        const void *shared_gate, *shared_up, *shared_down; const void *norm_weight;
+ *                        int64_t *topk_indices; void *topk_weights; void *gammas;    (optional outputs, may be null)
+ *                        float route_scale; int pad; }
+ *  x            BF16 [hidden]: input of the first block
+ *  glue = 0     n_layers must be 1; partial_out FP32 [hidden] receives the block's output
+ *  glue = 1     residual_io BF16 [hidden] is the residual stream (updated in place),
+ *               normed_out BF16 [hidden] the normalised output after the last block,
+ *               partial_out the last block's FP32 output
+ *  scratch      ink_moe_stack_scratch_bytes(...) bytes, contents irrelevant at entry
+ *  status       optional int32 word: bit 1 is set if a bounded wait inside the kernel gave up
+ * Built shapes (hidden, intermediate): (4096, 2048|1024|512|256), (2048, 256), (1024, 512);
+ * experts <= 512, top_k <= 8, n_shared <= 2. The device must support cooperative launches.
+ */
+size_t ink_moe_stack_layer_bytes(void);
+/* Tracing (the reference's counterpart is utils/profiling.py:36-78): with the environment
+ * variable INKLING_STACK_TRACE=1 every block stamps its phase boundaries with the global
+ * nanosecond timer into the scratch at this byte offset, laid out
+ * [n_layers][256 blocks][16 slots] of uint64 (slot meanings: enum TraceSlot in moe_stack.cu). */
+size_t ink_moe_stack_trace_offset(int n_layers, int hidden, int intermediate, int experts, int n_shared,
+                                  int top_k);
+size_t ink_moe_stack_scratch_bytes(int n_layers, int hidden, int intermediate, int experts, int n_shared,
+                                   int top_k);
+int ink_moe_stack_decode(const void* layers, int n_layers, const void* x, void* residual_io, void* normed_out,
+                         float* partial_out, int glue, float eps, int hidden, int intermediate, int experts,
+                         int n_shared, int top_k, void* scratch, size_t scratch_bytes, int32_t* status,
+                         ink_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

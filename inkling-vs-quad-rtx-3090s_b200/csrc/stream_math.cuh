@@ -1,0 +1,84 @@
+// Per-warp arithmetic shared by the streaming kernels: NVFP4 and BF16 dot products on
+// shared-memory tiles, multi-row warp reductions, activation staging.
+#pragma once
+#include "common.cuh"
+
+namespace ink {
+
+// 32 weights x 32 FP16 activations with their two block scales -> FP32
+__device__ __forceinline__ float dot32(const uint4& q, uint32_t scale_pair, const uint32_t* x) {
+  uint32_t h[4];
+  uint32_t a0 = 0u, a1 = 0u;
+  e2m1x8_to_f16x2(q.x, h);
+  a0 = hfma2(h[0], x[0], a0); a0 = hfma2(h[1], x[1], a0); a0 = hfma2(h[2], x[2], a0); a0 = hfma2(h[3], x[3], a0);
+  e2m1x8_to_f16x2(q.y, h);
+  a0 = hfma2(h[0], x[4], a0); a0 = hfma2(h[1], x[5], a0); a0 = hfma2(h[2], x[6], a0); a0 = hfma2(h[3], x[7], a0);
+  e2m1x8_to_f16x2(q.z, h);
+  a1 = hfma2(h[0], x[8], a1); a1 = hfma2(h[1], x[9], a1); a1 = hfma2(h[2], x[10], a1); a1 = hfma2(h[3], x[11], a1);
+  e2m1x8_to_f16x2(q.w, h);
+  a1 = hfma2(h[0], x[12], a1); a1 = hfma2(h[1], x[13], a1); a1 = hfma2(h[2], x[14], a1); a1 = hfma2(h[3], x[15], a1);
+  const uint32_t s = e4m3x2_to_f16x2((uint16_t)scale_pair);
+  const float b0 = f16lo_to_f32(a0) + f16hi_to_f32(a0);
+  const float b1 = f16lo_to_f32(a1) + f16hi_to_f32(a1);
+  return fmaf(f16lo_to_f32(s), b0, f16hi_to_f32(s) * b1);
+}
+
+// 8 BF16 weights x 8 BF16 activations, FP32 accumulate
+__device__ __forceinline__ float dot8(const uint4& w, const uint4& x, float acc) {
+  acc = fmaf(bf16lo(w.x), bf16lo(x.x), acc); acc = fmaf(bf16hi(w.x), bf16hi(x.x), acc);
+  acc = fmaf(bf16lo(w.y), bf16lo(x.y), acc); acc = fmaf(bf16hi(w.y), bf16hi(x.y), acc);
+  acc = fmaf(bf16lo(w.z), bf16lo(x.z), acc); acc = fmaf(bf16hi(w.z), bf16hi(x.z), acc);
+  acc = fmaf(bf16lo(w.w), bf16lo(x.w), acc); acc = fmaf(bf16hi(w.w), bf16hi(x.w), acc);
+  return acc;
+}
+
+// Sums R per-lane values over the 32 lanes in R/2 + R/4 + ... + (5 - log2 R) shuffles.
+// Every lane returns the total of row `reduced_row<R>(lane)`.
+template <int R>
+__device__ __forceinline__ float multi_reduce(float (&v)[R], int lane) {
+  int o = 16;
+#pragma unroll
+  for (int n = R; n > 1; n >>= 1, o >>= 1) {
+    const bool upper = (lane & o) != 0;
+#pragma unroll
+    for (int i = 0; i < n / 2; ++i) {
+      const float send = upper ? v[i] : v[i + n / 2];
+      const float keep = upper ? v[i + n / 2] : v[i];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+    }
+  }
+#pragma unroll
+  for (; o > 0; o >>= 1) v[0] += __shfl_xor_sync(0xffffffffu, v[0], o);
+  return v[0];
+}
+template <int R>
+__device__ __forceinline__ int reduced_row(int lane) {
+  int row = 0, o = 16;
+#pragma unroll
+  for (int n = R; n > 1; n >>= 1, o >>= 1) row += (lane & o) ? n / 2 : 0;
+  return row;
+}
+template <int R>
+__device__ __forceinline__ bool reduced_owner(int lane) {  // one lane per row
+  return (lane & ((32 / R) - 1)) == 0;
+}
+
+// One warp: K BF16 values -> FP16 scaled by a power of two into [1, 2); returns the inverse.
+__device__ __forceinline__ float warp_stage_f16(const uint16_t* src, uint16_t* dst, int k, int lane) {
+  uint32_t amax = 0;
+  for (int i = lane; i < k / 2; i += 32) {
+    const uint32_t v = reinterpret_cast<const uint32_t*>(src)[i];
+    amax = max(amax, max(v & 0x7fffu, (v >> 16) & 0x7fffu));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  float inverse;
+  const float scale = pow2_normaliser(amax, &inverse);
+  for (int i = lane; i < k / 2; i += 32) {
+    const uint32_t v = reinterpret_cast<const uint32_t*>(src)[i];
+    reinterpret_cast<uint32_t*>(dst)[i] = f32x2_to_f16x2(bf16lo(v) * scale, bf16hi(v) * scale);
+  }
+  return inverse;
+}
+
+}  // namespace ink

@@ -3,6 +3,7 @@ routed-expert path: same names, same call signatures, sm_100a library underneath
 from .expert_planner import expert_copy, expert_plan
 from .grouped_experts import expert_bank_names
 from .routed_decode import add_rmsnorm, moe_decode, routed_decode
+from .stack import StackDescriptor, stack_supported
 from .router import router_forward, router_plan_forward, router_workspace
 
 __all__ = [
@@ -12,6 +13,8 @@ __all__ = [
     "expert_plan",
     "moe_decode",
     "routed_decode",
+    "StackDescriptor",
+    "stack_supported",
     "router_forward",
     "router_plan_forward",
     "router_workspace",

@@ -29,6 +29,10 @@ _SIGNATURES = {
     "ink_moe_gate_up": (I, [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P, P]),
     "ink_moe_down": (I, [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P, P]),
     "ink_add_rmsnorm": (I, [P, P, P, F, P, I, I, P]),
+    "ink_moe_stack_layer_bytes": (Z, []),
+    "ink_moe_stack_scratch_bytes": (Z, [I, I, I, I, I, I]),
+    "ink_moe_stack_trace_offset": (Z, [I, I, I, I, I, I]),
+    "ink_moe_stack_decode": (I, [P, I, P, P, P, P, I, F, I, I, I, I, I, P, Z, P, P]),
 }
 
 

@@ -1,0 +1,71 @@
+"""One-launch decode of a stack of MoE blocks (ink_moe_stack_decode)."""
+from __future__ import annotations
+
+import struct
+
+import torch
+
+from . import _abi
+
+BUILT_SHAPES = {(4096, 2048), (4096, 1024), (4096, 512), (4096, 256), (2048, 256), (1024, 512)}
+_LAYER_FORMAT = "<11Qfi"   # eleven pointers, route_scale, pad
+
+
+def stack_supported(hidden: int, intermediate: int, experts: int, n_shared: int, top_k: int) -> bool:
+    return ((hidden, intermediate) in BUILT_SHAPES and experts <= 512 and top_k <= 8 and n_shared <= 2
+            and top_k <= experts)
+
+
+class StackDescriptor:
+    """Device-side table of block descriptors plus the kernel's scratch; built once."""
+
+    def __init__(self, blocks: list[dict], hidden: int, intermediate: int, experts: int, n_shared: int,
+                 top_k: int, device):
+        assert struct.calcsize(_LAYER_FORMAT) == _abi.lib().ink_moe_stack_layer_bytes()
+        self.keep = blocks   # the tensors the addresses point into
+        self.n_layers, self.hidden, self.intermediate = len(blocks), hidden, intermediate
+        self.experts, self.n_shared, self.top_k = experts, n_shared, top_k
+        ptr = lambda t: 0 if t is None else t.data_ptr()  # noqa: E731
+        raw = b"".join(struct.pack(
+            _LAYER_FORMAT, ptr(b["router_weight"]), ptr(b["router_bias"]), ptr(b["global_scale"]), ptr(b["sources"]),
+            ptr(b["shared_gate"]), ptr(b["shared_up"]), ptr(b["shared_down"]), ptr(b.get("norm_weight")),
+            ptr(b.get("topk_indices")), ptr(b.get("topk_weights")), ptr(b.get("gammas")), float(b["route_scale"]), 0)
+            for b in blocks)
+        self.table = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(device)
+        size = _abi.lib().ink_moe_stack_scratch_bytes(self.n_layers, hidden, intermediate, experts, n_shared, top_k)
+        self.scratch = torch.zeros(size, dtype=torch.uint8, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def decode(self, x, partial_out, residual_io=None, normed_out=None, eps: float = 1e-6) -> None:
+        glue = residual_io is not None
+        assert x.dtype == torch.bfloat16 and x.numel() == self.hidden and x.is_contiguous()
+        assert partial_out.dtype == torch.float32 and partial_out.numel() == self.hidden
+        if glue:
+            assert residual_io.dtype == normed_out.dtype == torch.bfloat16
+            assert residual_io.numel() == normed_out.numel() == self.hidden
+        _abi.require_cuda(x, partial_out, residual_io, normed_out)
+        _abi.check(_abi.lib().ink_moe_stack_decode(
+            self.table.data_ptr(), self.n_layers, x.data_ptr(), _abi.ptr(residual_io), _abi.ptr(normed_out),
+            partial_out.data_ptr(), int(glue), float(eps), self.hidden, self.intermediate, self.experts,
+            self.n_shared, self.top_k, self.scratch.data_ptr(), self.scratch.numel(), self.status.data_ptr(),
+            _abi.stream()))
+
+    def check_status(self) -> None:
+        """Host read (synchronises): raises if a bounded wait inside the kernel gave up."""
+        flags = int(self.status.item())
+        self.status.zero_()
+        if flags & 2:
+            raise RuntimeError("moe_stack: a bounded wait inside the kernel timed out; the output is invalid")
+
+    TRACE_SLOTS = ("layer_start", "router_rows_done", "shared_gate_up_done", "routed_gate_up_done",
+                   "shared_gate_up_everywhere", "shared_down_done", "routed_gate_up_everywhere", "activations_staged",
+                   "routed_down_done", "down_everywhere", "norm_done", "", "producer_waits_for_routing",
+                   "producer_has_routing", "producer_layer_issued", "")
+
+    def trace(self) -> torch.Tensor:
+        """Phase stamps of the last decode run with INKLING_STACK_TRACE=1: int64
+        [n_layers, 256, 16] nanoseconds (zero where a block did not stamp). Synchronises."""
+        offset = _abi.lib().ink_moe_stack_trace_offset(self.n_layers, self.hidden, self.intermediate, self.experts,
+                                                       self.n_shared, self.top_k)
+        raw = self.scratch[offset:offset + self.n_layers * 256 * 16 * 8].clone()
+        return raw.view(torch.int64).view(self.n_layers, 256, 16).cpu()

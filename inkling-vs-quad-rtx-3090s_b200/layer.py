@@ -17,8 +17,8 @@ from __future__ import annotations
 import torch
 from torch import nn
 
-from .kernels import (expert_bank_names, expert_copy, expert_plan, moe_decode, routed_decode,
-                      router_forward, router_plan_forward, router_workspace)
+from .kernels import (StackDescriptor, expert_bank_names, expert_copy, expert_plan, moe_decode, routed_decode,
+                      router_forward, router_plan_forward, router_workspace, stack_supported)
 from .kernels.paired_all_reduce import all_reduce
 
 # Up to this many tokens each route runs its own matrix-vector product
@@ -140,12 +140,33 @@ class FusedMoE(nn.Module):
         self.experts = experts
         self.device_mesh = device_mesh
         self._tokens = 0
+        self._fused = None   # one-launch descriptor for a single token, built on first use
+
+    def block_descriptor(self, norm_weight=None) -> dict:
+        """This block as the one-launch kernel takes it (addresses of the module's tensors)."""
+        self._reserve(1)
+        ex = self.experts
+        return dict(router_weight=self.router_weight, router_bias=self.router_bias, global_scale=self.global_scale,
+                    sources=ex.sources, shared_gate=self.shared_gate, shared_up=self.shared_up,
+                    shared_down=self.shared_down, norm_weight=norm_weight, topk_indices=self.topk_indices,
+                    topk_weights=self.topk_weights, gammas=self.gammas, route_scale=self.route_scale)
+
+    def one_launch_supported(self) -> bool:
+        ex = self.experts
+        world = 1
+        group = _group_of(self.device_mesh)
+        if group is not None and torch.distributed.is_initialized():
+            world = torch.distributed.get_world_size(group)
+        return (world == 1 and ex.start == 0 and
+                stack_supported(ex.hidden_dim, ex.intermediate_dim, ex.local, self.n_shared, self.top_k))
 
     def _reserve(self, tokens: int) -> None:
         if tokens <= self._tokens:
             return
         dev, bf = self.router_weight.device, torch.bfloat16
         self._tokens = tokens
+        self._fused = None          # descriptors hold addresses of the buffers replaced below
+        self.generation = getattr(self, "generation", 0) + 1
         self.topk_weights = torch.empty(tokens, self.top_k, dtype=bf, device=dev)
         self.topk_indices = torch.empty(tokens, self.top_k, dtype=torch.int64, device=dev)
         self.gammas = torch.empty(tokens, self.n_shared, dtype=bf, device=dev)
@@ -177,8 +198,14 @@ class FusedMoE(nn.Module):
         module's own buffer, overwritten by the next call)."""
         t = flat.shape[0]
         self._reserve(t)
-        self.route(flat)
         ex = self.experts
+        if t == 1 and self.one_launch_supported():
+            if self._fused is None:
+                self._fused = StackDescriptor([self.block_descriptor()], ex.hidden_dim, ex.intermediate_dim,
+                                              ex.local, self.n_shared, self.top_k, flat.device)
+            self._fused.decode(flat, self.partial[:1])
+            return self.partial[:1]
+        self.route(flat)
         for t0 in range(0, t, MATVEC_TOKENS):
             t1 = min(t, t0 + MATVEC_TOKENS)
             moe_decode(flat[t0:t1], self.topk_indices[t0:t1], self.topk_weights[t0:t1], ex.pointers,

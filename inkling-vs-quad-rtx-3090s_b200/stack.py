@@ -7,7 +7,7 @@ from __future__ import annotations
 import torch
 from torch import nn
 
-from .kernels import add_rmsnorm
+from .kernels import StackDescriptor, add_rmsnorm
 from .layer import FusedMoE, ResidentExperts
 from .synthetic import make_expert_banks, make_layer_params
 
@@ -20,6 +20,8 @@ class MoEStack(nn.Module):
         dev = layers[0].router_weight.device
         self.norm_weight = torch.ones(hidden, dtype=torch.bfloat16, device=dev)
         self._tokens = 0
+        self._fused = None
+        self.one_launch = all(layer.one_launch_supported() for layer in layers)
 
     @classmethod
     def synthetic(cls, n_layers: int, hidden: int, intermediate: int, experts: int, n_shared: int, top_k: int,
@@ -49,6 +51,17 @@ class MoEStack(nn.Module):
         self._reserve(t)
         residual, normed = self.residual[:t], self.normed[:t]
         residual.copy_(x)
+        if t == 1 and self.one_launch:
+            generations = tuple(layer.generation for layer in self.layers if hasattr(layer, "generation"))
+            if self._fused is None or self._fused_generations != generations:
+                first = self.layers[0]
+                ex = first.experts
+                blocks = [layer.block_descriptor(self.norm_weight) for layer in self.layers]
+                self._fused = StackDescriptor(blocks, ex.hidden_dim, ex.intermediate_dim, ex.local, first.n_shared,
+                                              first.top_k, x.device)
+                self._fused_generations = tuple(layer.generation for layer in self.layers)
+            self._fused.decode(x, self.layers[-1].partial[:1], residual, normed, self.eps)
+            return normed
         normed.copy_(x)
         for layer in self.layers:
             add_rmsnorm(layer.forward_partial(normed), residual, self.norm_weight, self.eps, normed)
@@ -56,6 +69,8 @@ class MoEStack(nn.Module):
 
     def launches_per_step(self) -> int:
         """Kernels of this library launched by one forward of one token batch <= 8."""
+        if self.one_launch:
+            return 1                  # the whole stack is one persistent kernel
         return 4 * len(self.layers)   # router+plan, gate/up, down, add+norm
 
 

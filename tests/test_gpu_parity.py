@@ -355,7 +355,13 @@ def test_baseline_shape_against_oracle(ib, device, baseline_layer):
     cpu_banks = {int(e): {n: t.cpu() for n, t in banks.weights[int(e)].items()} for e in idx.flatten()}
     want = oracle_moe.moe_layer_fp32(x, p, cpu_banks, idx, w, gam)
     assert max_rel(out.float(), want) <= TOL
-    act_ref, routed_ref = oracle_moe.routed_decode_reference(x, idx, w, cpu_banks)
+    # the launch-by-launch path (two tokens) leaves the gate/up activations in the module's scratch
+    x2 = torch.cat([x, x])
+    layer(x2.to(device).unsqueeze(0))
+    torch.cuda.synchronize()
+    idx2, w2 = layer.topk_indices[:1].cpu(), layer.topk_weights[:1].cpu()
+    banks2 = {int(e): {n: t.cpu() for n, t in banks.weights[int(e)].items()} for e in idx2.flatten()}
+    act_ref, routed_ref = oracle_moe.routed_decode_reference(x, idx2, w2, banks2)
     assert max_rel(layer.experts.activated[:6].cpu().float(), act_ref.float()) <= 8e-3
 
 
