@@ -60,6 +60,25 @@ int ink_router_forward(const void* x, const void* weight, const float* bias, con
                        void* shared_gammas, void* workspace, size_t workspace_bytes,
                        ink_stream_t stream);
 
+/* The router for callers that cannot allocate device memory -- code that runs inside an
+ * allocator callback or under a framework's memory plan that was fixed at start-up, a
+ * host thread that must not take the allocator's lock, a process whose memory budget is
+ * frozen once the model is resident. It has no counterpart in the reference. Same
+ * arithmetic and outputs as ink_router_forward, but the kernel's scratch (block counter,
+ * logits, selection scores: 35 072 bytes) is an array inside the library image instead
+ * of a caller buffer, so every GPU the process uses holds those bytes until exit.
+ * Limits: tokens <= 8 and n_routed + n_shared <= 544; anything larger is refused with an
+ * error. It calls no cudaMalloc/cudaFree and no allocating library routine. The first call
+ * on each device looks the array's device address up (cudaGetSymbolAddress); make that
+ * first call outside stream capture. All calls share the one array and the kernel reads
+ * what the previous call left there only after re-zeroing the counter, so calls must not
+ * overlap on the GPU (issue them on one stream, or order them yourself): two calls in
+ * flight at once race on the scratch. */
+int ink_router_forward_static(const void* x, const void* weight, const float* bias, const void* global_scale,
+                              float route_scale, int tokens, int hidden, int n_routed, int n_shared, int top_k,
+                              void* routed_logits, void* topk_weights, int64_t* topk_indices,
+                              void* shared_gammas, ink_stream_t stream);
+
 /* Router and expert plan in ONE launch (decode: tokens * top_k <= 512 routes); the
  * plan arguments are those of ink_expert_plan below. */
 int ink_router_plan_forward(const void* x, const void* weight, const float* bias, const void* global_scale,

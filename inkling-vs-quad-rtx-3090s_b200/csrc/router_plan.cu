@@ -403,6 +403,51 @@ extern "C" int ink_router_forward(const void* x, const void* weight, const float
   return kOk;
 }
 
+// ------------------------------------------------------------ router, no allocation
+// Scratch for ink_router_forward_static: lives in the library image, so a process that
+// loads the library holds these bytes on every GPU it uses, until it exits.
+constexpr int kStaticRouterTokens = 8;
+constexpr int kStaticRouterExperts = 32 * kMaxScoresPerLane + 32;   // routed + shared rows at most
+constexpr size_t kStaticRouterBytes = 256 + 2 * sizeof(float) * kStaticRouterTokens * kStaticRouterExperts;
+static __device__ __align__(256) unsigned char g_static_router_scratch[kStaticRouterBytes];
+
+constexpr int kStaticMaxDevices = 64;
+static void* g_static_router_ptr[kStaticMaxDevices];   // device address of the array, per device ordinal
+
+extern "C" int ink_router_forward_static(const void* x, const void* weight, const float* bias,
+                                         const void* global_scale, float route_scale, int tokens, int hidden,
+                                         int n_routed, int n_shared, int top_k, void* routed_logits,
+                                         void* topk_weights, int64_t* topk_indices, void* shared_gammas,
+                                         ink_stream_t stream) {
+  INK_REQUIRE(tokens >= 0 && tokens <= kStaticRouterTokens, kUnsupportedShape,
+              "router (static scratch): %d tokens, the built-in scratch holds at most %d", tokens,
+              kStaticRouterTokens);
+  INK_REQUIRE(n_routed > 0 && n_shared >= 0 && n_routed + n_shared <= kStaticRouterExperts, kUnsupportedShape,
+              "router (static scratch): %d router rows, the built-in scratch holds at most %d",
+              n_routed + n_shared, kStaticRouterExperts);
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  INK_REQUIRE(e == cudaSuccess && device >= 0 && device < kStaticMaxDevices, kLaunchFailed,
+              "router (static scratch): cannot identify the current device: %s", cudaGetErrorString(e));
+  if (g_static_router_ptr[device] == nullptr) {
+    // The array's name is only a handle on the host: ask the runtime for its address on
+    // the device that is current now, once, and keep it.
+    void* address = nullptr;
+    e = cudaGetSymbolAddress(&address, g_static_router_scratch);
+    INK_REQUIRE(e == cudaSuccess && address != nullptr, kLaunchFailed,
+                "router (static scratch): cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    g_static_router_ptr[device] = address;
+  }
+  void* scratch = g_static_router_ptr[device];
+  // The block counter at the head of the scratch must be zero when the kernel starts; the
+  // previous call normally leaves it so, but a call that was cut short would not.
+  e = cudaMemsetAsync(scratch, 0, 256, (cudaStream_t)stream);
+  INK_REQUIRE(e == cudaSuccess, kLaunchFailed, "router (static scratch): memset failed: %s", cudaGetErrorString(e));
+  return ink_router_forward(x, weight, bias, global_scale, route_scale, tokens, hidden, n_routed, n_shared, top_k,
+                            routed_logits, topk_weights, topk_indices, shared_gammas, scratch, kStaticRouterBytes,
+                            stream);
+}
+
 extern "C" int ink_router_plan_forward(const void* x, const void* weight, const float* bias,
                                        const void* global_scale, float route_scale, int tokens, int hidden,
                                        int n_routed, int n_shared, int top_k, void* routed_logits,

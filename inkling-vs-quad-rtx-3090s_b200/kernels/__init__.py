@@ -4,7 +4,7 @@ from .expert_planner import expert_copy, expert_plan
 from .grouped_experts import expert_bank_names
 from .routed_decode import add_rmsnorm, moe_decode, routed_decode
 from .stack import StackDescriptor, stack_supported
-from .router import router_forward, router_plan_forward, router_workspace
+from .router import router_forward, router_forward_static, router_plan_forward, router_workspace
 
 __all__ = [
     "add_rmsnorm",
@@ -16,6 +16,7 @@ __all__ = [
     "StackDescriptor",
     "stack_supported",
     "router_forward",
+    "router_forward_static",
     "router_plan_forward",
     "router_workspace",
 ]

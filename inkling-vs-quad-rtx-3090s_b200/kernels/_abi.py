@@ -21,6 +21,7 @@ _SIGNATURES = {
     "ink_abi_version": (I, []),
     "ink_router_workspace_bytes": (Z, [I, I]),
     "ink_router_forward": (I, [P, P, P, P, F, I, I, I, I, I, P, P, P, P, P, Z, P]),
+    "ink_router_forward_static": (I, [P, P, P, P, F, I, I, I, I, I, P, P, P, P, P]),
     "ink_router_plan_forward": (I, [P, P, P, P, F, I, I, I, I, I, P, P, P, P, P, Z,
                                     P, P, P, P, P, I, I, I, I, P]),
     "ink_expert_plan": (I, [P, P, P, P, P, P, I, I, I, I, I, P]),

@@ -48,3 +48,18 @@ def router_plan_forward(x, weight, bias, global_scale, route_scale: float, top_k
         topk_indices.data_ptr(), shared_gammas.data_ptr(), workspace.data_ptr(), workspace.numel(),
         sources.data_ptr(), pointers.data_ptr(), experts.data_ptr(), counts.data_ptr(), rows.data_ptr(),
         start, local, stride, capacity, _abi.stream()))
+
+
+def router_forward_static(x, weight, bias, global_scale, route_scale: float, top_k: int, n_shared: int,
+                          topk_weights, topk_indices, shared_gammas, routed_logits=None) -> None:
+    """`router_forward` without a workspace argument, for callers that may not allocate
+    device memory: the kernel's scratch is an array inside the library (at most 8 tokens
+    and 544 router rows). Calls share that array, so keep them on one stream; make the
+    first call on a device outside graph capture (it looks the array's address up)."""
+    workspace = topk_weights   # only to satisfy the shared argument checks; not passed on
+    tokens, hidden, n_routed = _common(x, weight, bias, global_scale, top_k, n_shared, topk_weights,
+                                       topk_indices, shared_gammas, workspace)
+    _abi.check(_abi.lib().ink_router_forward_static(
+        x.data_ptr(), weight.data_ptr(), bias.data_ptr(), global_scale.data_ptr(), float(route_scale), tokens,
+        hidden, n_routed, n_shared, top_k, _abi.ptr(routed_logits), topk_weights.data_ptr(),
+        topk_indices.data_ptr(), shared_gammas.data_ptr(), _abi.stream()))
