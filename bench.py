@@ -310,8 +310,7 @@ def run_ours(args) -> None:
     }
     barrier()
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+        leave(world)
         return
 
     peaks, peak_kind = load_peaks()
@@ -355,8 +354,16 @@ def run_ours(args) -> None:
             "sample": f"median of 10 forwards of one block (config[0]) through the CPU oracle, {cores} threads; "
                       f"scaled to {layers} blocks per token", "block_seconds": seconds}
     print(json.dumps(line), flush=True)
+    leave(world)
+
+
+def leave(world: int) -> None:
+    """Multi-rank runs end here, after the last barrier: tearing an NCCL communicator down while
+    captured graphs still hold its kernels can block for minutes, so the ranks flush and exit."""
     if world > 1:
-        dist.destroy_process_group()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main() -> None:
