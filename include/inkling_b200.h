@@ -164,6 +164,34 @@ int ink_moe_down(const void* x, const int64_t* indices, const void* weights, con
 int ink_add_rmsnorm(const float* partial, void* residual, const void* weight, float eps, void* normed,
                     int tokens, int hidden, ink_stream_t stream);
 
+/* ------------------------------------------------------ grouped projections ------
+ * Replace the Triton kernels expert_gemm (kernels/grouped_experts.py:26-148) and
+ * expert_reduce (:152-186) for more than a handful of tokens, on the tcgen05 tensor cores.
+ * ink_expert_gemm: for every active group g (expert experts[g], routes rows[g, :counts[g]])
+ *   projection 0: y[route, j] = bf16(silu(gate) * up), gate/up = even/odd rows of
+ *                 W_gate_up[expert] . x[route / top_k]       (x BF16 [tokens, k], n = 2f rows)
+ *   projection 1: y[route, :] = bf16(W_down[expert] . x[route])   (x BF16 [capacity, k], n = d rows)
+ * FP32 accumulation in tensor memory. Weights enter the MMA as value * block scale in
+ * FP16, which is exact, and the per-bank FP32 scale multiplies the accumulator; the
+ * reference rounds value * (block scale * scale2) to BF16 first, so results agree to BF16
+ * rounding of the weights, not bit for bit.
+ *  input_rows  rows of x (tokens for projection 0, capacity for projection 1)
+ *  groups      number of entries of experts/counts to visit (inactive ones cost nothing)
+ *  scratch     ink_expert_gemm_scratch_bytes(input_rows) bytes
+ * Constraints: NVFP4 banks; k a multiple of 128, at most 8192; n even.
+ * ink_expert_reduce: output[token] += sum over choices of fp32(bf16(down[route] * w)),
+ * skipping routes whose pointer row is zero; output FP32 [tokens, width], pre-zeroed by
+ * the caller as in the reference (my_inkling/offloaded_experts.py:304).
+ */
+size_t ink_expert_gemm_scratch_bytes(int input_rows);
+int ink_expert_gemm(const void* x, int input_rows, const int64_t* pointers, const int32_t* experts,
+                    const int32_t* rows, const int32_t* counts, void* y, int capacity, int n, int k, int top_k,
+                    int projection, int quantized, int groups, void* scratch, size_t scratch_bytes,
+                    int32_t* status, ink_stream_t stream);
+int ink_expert_reduce(const void* down, const int64_t* indices, const void* weights, const int64_t* pointers,
+                      float* output, int tokens, int width, int top_k, int pointer_stride, int max_expert,
+                      ink_stream_t stream);
+
 /* ------------------------------------------------- whole stack, one launch ------
  * One decode token through n_layers MoE blocks in ONE persistent cooperative kernel:
  * per block the router (as ink_router_forward), the expert plan (resolved to bank

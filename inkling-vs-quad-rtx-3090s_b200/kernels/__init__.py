@@ -1,7 +1,7 @@
 """Drop-in counterpart of the reference's `kernels` package for the NVFP4
 routed-expert path: same names, same call signatures, sm_100a library underneath."""
 from .expert_planner import expert_copy, expert_plan
-from .grouped_experts import expert_bank_names
+from .grouped_experts import expert_bank_names, expert_gemm, expert_reduce
 from .routed_decode import add_rmsnorm, moe_decode, routed_decode
 from .stack import StackDescriptor, stack_supported
 from .router import router_forward, router_forward_static, router_plan_forward, router_workspace
@@ -10,6 +10,8 @@ __all__ = [
     "add_rmsnorm",
     "expert_bank_names",
     "expert_copy",
+    "expert_gemm",
+    "expert_reduce",
     "expert_plan",
     "moe_decode",
     "routed_decode",

@@ -30,6 +30,9 @@ _SIGNATURES = {
     "ink_moe_gate_up": (I, [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P, P]),
     "ink_moe_down": (I, [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P, P]),
     "ink_add_rmsnorm": (I, [P, P, P, F, P, I, I, P]),
+    "ink_expert_gemm_scratch_bytes": (Z, [I]),
+    "ink_expert_gemm": (I, [P, I, P, P, P, P, P, I, I, I, I, I, I, I, P, Z, P, P]),
+    "ink_expert_reduce": (I, [P, P, P, P, P, I, I, I, I, I, P]),
     "ink_moe_stack_layer_bytes": (Z, []),
     "ink_moe_stack_scratch_bytes": (Z, [I, I, I, I, I, I]),
     "ink_moe_stack_trace_offset": (Z, [I, I, I, I, I, I]),

@@ -17,8 +17,9 @@ from __future__ import annotations
 import torch
 from torch import nn
 
-from .kernels import (StackDescriptor, expert_bank_names, expert_copy, expert_plan, moe_decode, routed_decode,
-                      router_forward, router_plan_forward, router_workspace, stack_supported)
+from .kernels import (StackDescriptor, expert_bank_names, expert_copy, expert_gemm, expert_plan, expert_reduce,
+                      moe_decode, routed_decode, router_forward, router_plan_forward, router_workspace,
+                      stack_supported)
 from .kernels.paired_all_reduce import all_reduce
 
 # Up to this many tokens each route runs its own matrix-vector product
@@ -30,6 +31,10 @@ def _group_of(device_mesh):
     if device_mesh is None:
         return None
     return device_mesh.get_group() if hasattr(device_mesh, "get_group") else device_mesh
+
+
+def triton_cdiv(a: int, b: int) -> int:
+    return (a + b - 1) // b
 
 
 def _next_pow2(n: int) -> int:
@@ -98,8 +103,27 @@ class ResidentExperts(nn.Module):
                           _next_pow2(self.local), 1, _next_pow2(routes), num_warps=4)
         expert_copy[(128, 0)](self.sources, self.destinations, self.copy_experts, (), self.stride, 1024, 128)
 
+    def grouped_supported(self) -> bool:
+        """The tensor-core path needs both contraction widths to be multiples of 128."""
+        return self.hidden_dim % 128 == 0 and self.intermediate_dim % 128 == 0
+
     def _project(self, x, indices, weights, output) -> None:
+        """GEMV per route up to MATVEC_TOKENS tokens, grouped tensor-core GEMMs above
+        (my_inkling/offloaded_experts.py:224-296). `output` must be zero on entry."""
         tokens = x.shape[0]
+        if tokens > MATVEC_TOKENS and self.grouped_supported():
+            routes, top_k = indices.numel(), indices.shape[1]
+            groups = min(routes, self.local)
+            for projection, inputs, target, n, k in (
+                    (0, x, self.activated, 2 * self.intermediate_dim, self.hidden_dim),
+                    (1, self.activated, self.down, self.hidden_dim, self.intermediate_dim)):
+                grid = (triton_cdiv(routes, 16), triton_cdiv(n, 64), groups)
+                expert_gemm[grid](inputs, self.pointers, self.experts, self.rows, self.counts, target, self.capacity,
+                                  n, k, top_k, projection, True, self.stride, 16, 64, 64, status=self.status)
+            expert_reduce[(tokens, triton_cdiv(self.hidden_dim, 256))](
+                self.down, indices, weights, self.pointers, output, self.hidden_dim, top_k, self.stride,
+                self.max_expert, 256)
+            return
         for t0 in range(0, tokens, MATVEC_TOKENS):
             t1 = min(tokens, t0 + MATVEC_TOKENS)
             routed_decode(x[t0:t1], indices[t0:t1], weights[t0:t1], self.pointers,
@@ -107,7 +131,7 @@ class ResidentExperts(nn.Module):
                           status=self.status)
 
     def forward(self, hidden_states, top_k_index, top_k_weights):
-        final = torch.empty_like(hidden_states, dtype=torch.float32)
+        final = torch.zeros_like(hidden_states, dtype=torch.float32)
         self._reserve(top_k_index.numel())
         self._plan(top_k_index)
         self._project(hidden_states.contiguous(), top_k_index.contiguous(), top_k_weights.contiguous(), final)
@@ -192,6 +216,16 @@ class FusedMoE(nn.Module):
         shape = hidden_states.shape
         flat = hidden_states.reshape(-1, shape[-1]).contiguous()
         return self.forward_partial(flat).to(hidden_states.dtype).view(shape)
+
+    def _shared_experts(self, flat, gammas):
+        """my_inkling/model.py:192-226 with torch's BF16 GEMMs: gate/up, silu * up * gamma, down,
+        FP32 sum over the shared experts, one BF16 rounding."""
+        h = flat.unsqueeze(0).expand(self.n_shared, -1, -1)
+        gate = torch.bmm(h, self.shared_gate.transpose(1, 2))
+        up = torch.bmm(h, self.shared_up.transpose(1, 2))
+        activated = torch.nn.functional.silu(gate) * up * gammas.T.unsqueeze(-1)
+        down = torch.bmm(activated, self.shared_down.transpose(1, 2))
+        return down.float().sum(dim=0).to(flat.dtype)
 
     def forward_partial(self, flat):
         """flat BF16 [t, d] -> the all-reduced FP32 layer output [t, d] (a view of the
