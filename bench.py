@@ -357,6 +357,61 @@ def run_ours(args) -> None:
     leave(world)
 
 
+def run_batched(args) -> None:
+    """configs[3]: 64 tokens through ONE block of the full shapes, routing skewed by Zipf(1.1):
+    the grouped tensor-core path against the per-route GEMV path on the same routing. Prints its
+    own JSON line (not the headline metric)."""
+    import torch
+
+    import inkling_b200 as ib
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    tokens = 64
+    layers = [ib.MoEStack.synthetic(1, HIDDEN, INTERMEDIATE, EXPERTS, N_SHARED, TOP_K, device, seed=100 + i).layers[0]
+              for i in range(4)]          # rotate blocks so that nothing is L2-warm
+    gen = torch.Generator().manual_seed(7)
+    probs = 1.0 / torch.arange(1, EXPERTS + 1).float() ** 1.1
+    perm = torch.randperm(EXPERTS, generator=gen)
+    idx = torch.stack([perm[torch.multinomial(probs, TOP_K, replacement=False, generator=gen)] for _ in range(tokens)])
+    idx = idx.to(device)
+    w = torch.rand(tokens, TOP_K, generator=gen).to(torch.bfloat16).to(device)
+    x = torch.randn(tokens, HIDDEN, generator=gen).to(torch.bfloat16).to(device)
+    distinct = int(torch.unique(idx).numel())
+
+    def timed(fn):
+        for layer in layers:
+            fn(layer)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            for layer in layers:
+                fn(layer)
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / (args.steps * len(layers))
+
+    grouped_ms = timed(lambda layer: layer.experts(x, idx, w))
+
+    def gemv(layer):
+        for i in range(0, tokens, 8):
+            layer.experts(x[i:i + 8], idx[i:i + 8], w[i:i + 8])
+
+    gemv_ms = timed(gemv)
+    expert_bytes = 2 * INTERMEDIATE * HIDDEN // 2 + 2 * INTERMEDIATE * HIDDEN // 16 + HIDDEN * INTERMEDIATE // 2 + HIDDEN * INTERMEDIATE // 16
+    peaks, peak_kind = load_peaks()
+    print(json.dumps({
+        "metric": "batched_decode_block_ms", "value": grouped_ms, "unit": "ms", "higher_is_better": False,
+        "n_gpus": 1, "steps": args.steps, "data": "synthetic",
+        "config": {"workload": "configs[3]: one block, 64 tokens, Zipf(1.1) routing, routed experts only",
+                   "tokens": tokens, "distinct_experts": distinct, "routes": tokens * TOP_K},
+        "grouped_tcgen05_ms": grouped_ms, "gemv_per_route_ms": gemv_ms,
+        "grouped_weight_gbs": distinct * expert_bytes / (grouped_ms * 1e-3) / 1e9,
+        "gemv_weight_gbs": tokens * TOP_K * expert_bytes / (gemv_ms * 1e-3) / 1e9,
+        "peak_gbs": peaks["hbm_gbs"], "peak_kind": peak_kind}), flush=True)
+
+
 def leave(world: int) -> None:
     """Multi-rank runs end here, after the last barrier: tearing an NCCL communicator down while
     captured graphs still hold its kernels can block for minutes, so the ranks flush and exit."""
@@ -375,9 +430,12 @@ def main() -> None:
     parser.add_argument("--layers", type=int, default=40)
     parser.add_argument("--no-graph", action="store_true", help="eager launches instead of graph replay")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--batched", action="store_true", help="configs[3] instead of the headline workload")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.impl == "reference":
+    if args.batched:
+        run_batched(args)
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_ours(args)

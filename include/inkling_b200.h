@@ -211,7 +211,9 @@ int ink_expert_reduce(const void* down, const int64_t* indices, const void* weig
  *  glue = 1     residual_io BF16 [hidden] is the residual stream (updated in place),
  *               normed_out BF16 [hidden] the normalised output after the last block,
  *               partial_out the last block's FP32 output
- *  scratch      ink_moe_stack_scratch_bytes(...) bytes, contents irrelevant at entry
+ *  scratch      ink_moe_stack_scratch_bytes(...) bytes, ZERO-FILLED once before the first call and then
+ *               left alone: its counters only grow (each launch reads how many launches came before).
+ *               After a launch that reported a timed-out wait, zero it again before reuse.
  *  status       optional int32 word: bit 1 is set if a bounded wait inside the kernel gave up
  * Built shapes (hidden, intermediate): (4096, 2048|1024|512|256), (2048, 256), (1024, 512);
  * experts <= 512, top_k <= 8, n_shared <= 2. The device must support cooperative launches.
@@ -229,6 +231,26 @@ int ink_moe_stack_decode(const void* layers, int n_layers, const void* x, void* 
                          float* partial_out, int glue, float eps, int hidden, int intermediate, int experts,
                          int n_shared, int top_k, void* scratch, size_t scratch_bytes, int32_t* status,
                          ink_stream_t stream);
+
+/* The same across `world` tensor-parallel ranks (one process per GPU, experts cut on the FFN
+ * width, inputs and router replicated), with the all-reduce of every block done INSIDE the
+ * kernel: it stands in for the per-block all-reduce of my_inkling/offloaded_experts.py:310 and
+ * my_inkling/tp_plan.py:146 (kernels/paired_all_reduce.py:146-160). After the down projection
+ * every block stores its rows of the FP32 partial into a region of every rank (plain stores over
+ * NVLink into peer memory, then a system-scope release increment of that rank's counter); each
+ * rank sums the `world` deliveries in rank order, so all ranks get the same bits. Every rank
+ * launches this with the same arguments but its own layers/scratch and rank number.
+ *  peer_regions  host array of `world` addresses: region r is rank r's buffer of
+ *                ink_moe_stack_symmetric_bytes(n_layers, hidden, world) bytes as mapped into THIS
+ *                process (peer access enabled; e.g. torch symmetric memory). Zero-filled once on
+ *                every rank before any rank's first launch, then left alone like the scratch.
+ * All ranks must issue the same sequence of launches. Waits on other ranks are bounded like
+ * every other wait; no load with cluster scope touches peer memory. */
+size_t ink_moe_stack_symmetric_bytes(int n_layers, int hidden, int world);
+int ink_moe_stack_decode_tp(const void* layers, int n_layers, const void* x, void* residual_io, void* normed_out,
+                            float* partial_out, int glue, float eps, int hidden, int intermediate, int experts,
+                            int n_shared, int top_k, void* scratch, size_t scratch_bytes, int rank, int world,
+                            const uint64_t* peer_regions, int32_t* status, ink_stream_t stream);
 
 #ifdef __cplusplus
 }

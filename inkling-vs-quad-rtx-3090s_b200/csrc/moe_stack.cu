@@ -35,6 +35,7 @@ constexpr int kSMaxShared = 2;
 constexpr int kSMaxRows = 64;                          // output rows one block may own
 constexpr int kSMaxExperts = 512;
 constexpr int kSyncWordsPerLayer = 8;                  // counters of one layer
+constexpr int kSMaxWorld = 8;                          // tensor-parallel ranks
 
 constexpr int kTraceBlocks = 256;
 constexpr int kTraceSlots = 16;
@@ -55,7 +56,7 @@ __device__ __forceinline__ unsigned long long global_ns() {
       a.trace[((size_t)(layer) * kTraceBlocks + blockIdx.x) * kTraceSlots + (slot)] = global_ns();      \
   } while (0)
 
-enum SyncWord { kShGuDone = 0, kRtGuDone = 1, kDownDone = 2, kRouterRows = 3, kRouteReady = 4 };
+enum SyncWord { kShGuDone = 0, kRtGuDone = 1, kRouterRows = 3, kRouteReady = 4 };
 
 // What the layer's routing resolved to: written once per layer by the auxiliary warp
 // of one block, read by every producer and consumer.
@@ -106,7 +107,14 @@ struct StackArgs {
   uint16_t* activated;             // scratch [2][top_k][f]
   uint16_t* shared_activated;      // scratch [2][n_shared][f]
   RouteTable* routes;              // scratch [n_layers]
-  unsigned* sync;                  // scratch [n_layers][kSyncWordsPerLayer], zero at launch
+  unsigned* sync;                  // scratch [n_layers][kSyncWordsPerLayer]: counters that only grow (see epoch)
+  unsigned* epoch;                 // scratch: launches completed so far on this rank; every target scales with it
+  // tensor-parallel ranks (world == 1: the "peers" are this rank's own scratch)
+  int rank, world;
+  float* inbox;                    // this rank's [2][world][hidden] FP32: partial outputs as the ranks deliver them
+  unsigned* xsync;                 // this rank's [n_layers] counters of delivered blocks
+  float* peer_inbox[kSMaxWorld];   // the same two regions of every rank, as mapped into this process
+  unsigned* peer_xsync[kSMaxWorld];
   int32_t* status;
   unsigned long long* trace;       // optional [n_layers][kTraceBlocks][kTraceSlots] nanosecond stamps
 };
@@ -201,6 +209,7 @@ struct StackShared {
   float inverse[kSMaxTopK];             // inverse normalisers of the staged routed activations
   float x_inverse;                      // inverse normaliser of the staged x
   int done[2][3];                       // tiles finished per layer parity: shared g/u, routed g/u, down
+  unsigned epoch1;                      // launches completed before this one, plus one: scales every target
   volatile int tail_request;            // layer + 1 whose router tail this block must run
   volatile int failed;
 };
@@ -215,6 +224,15 @@ __device__ __forceinline__ void red_release_add(unsigned* p, unsigned v) {
 }
 __device__ __forceinline__ void st_release_u32(unsigned* p, unsigned v) {
   asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_sys_add(unsigned* p, unsigned v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 // Bounded wait for a global counter to reach `target`. One lane polls.
@@ -233,6 +251,22 @@ __device__ __forceinline__ bool wait_global(const unsigned* p, unsigned target, 
   return true;
 }
 
+// The same for a counter that other GPUs add to.
+__device__ __forceinline__ bool wait_system(const unsigned* p, unsigned target, StackShared* sh) {
+  if (sh->failed) return false;
+  if (ld_acquire_sys_u32(p) >= target) return true;
+  const long long t0 = clock64();
+  while (ld_acquire_u32(p) < target || ld_acquire_sys_u32(p) < target) {   // cheap poll first, system-scope acquire to finish
+    if (sh->failed) return false;
+    if (clock64() - t0 > kWaitLimitCycles) {
+      sh->failed = 1;
+      return false;
+    }
+    __nanosleep(32);
+  }
+  return true;
+}
+
 __device__ __forceinline__ void consumer_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(kSC * 32) : "memory");
 }
@@ -240,6 +274,7 @@ __device__ __forceinline__ void consumer_sync() {
 // -------------------------------------------------------------------- router tail
 // One warp. logits/scores of the layer are complete in global memory.
 __device__ void stack_router_tail(const StackArgs& a, const StackLayer& ly, int layer, StackShared* sh) {
+  const unsigned epoch1 = sh->epoch1;
   const int lane = threadIdx.x & 31;
   const int par = layer & 1;
   const float* logit = a.logits + (size_t)par * (a.experts + a.n_shared);
@@ -314,7 +349,7 @@ __device__ void stack_router_tail(const StackArgs& a, const StackLayer& ly, int 
   __syncwarp();
   if (lane == 0) {
     __threadfence();
-    st_release_u32(a.sync + (size_t)layer * kSyncWordsPerLayer + kRouteReady, 1u);
+    st_release_u32(a.sync + (size_t)layer * kSyncWordsPerLayer + kRouteReady, epoch1);
   }
 }
 
@@ -364,6 +399,7 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
     }
     sh.tail_request = 0;
     sh.failed = 0;
+    sh.epoch1 = *a.epoch + 1u;
     for (int i = 0; i < 6; ++i) (&sh.done[0][0])[i] = 0;
     mbar_init_fence();
   }
@@ -427,7 +463,7 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
         if (!alive) break;
         // ---- routing of this layer: wait, then bring the table into shared memory
         INK_TRACE(layer, kTrProdRouteWait);
-        if (!wait_global(sync + kRouteReady, 1u, &sh)) break;
+        if (!wait_global(sync + kRouteReady, sh.epoch1, &sh)) break;
         INK_TRACE(layer, kTrProdRouteGot);
         {
           const uint4* src = reinterpret_cast<const uint4*>(a.routes + layer);
@@ -500,7 +536,7 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
           break;
         }
         unsigned ready = 0;
-        if (lane == 0) ready = ld_acquire_u32(sync + kRouteReady);
+        if (lane == 0) ready = ld_acquire_u32(sync + kRouteReady) >= sh.epoch1;
         ready = __shfl_sync(0xffffffffu, ready, 0);
         if (ready || sh.failed) break;
         if (clock64() - t0 > 4 * kWaitLimitCycles) {
@@ -577,6 +613,11 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
       const uint16_t* norm_weight = a.layers[layer].norm_weight;
       unsigned* sync = a.sync + (size_t)layer * kSyncWordsPerLayer;
       const int par = layer & 1;
+      const unsigned epoch1 = sh.epoch1;
+      // slot of the ranks' deliveries: alternates with every block of every launch
+      const int xpar = (int)(((epoch1 - 1u) * (unsigned)a.n_layers + (unsigned)layer) & 1u);
+      float* inbox = a.inbox + (size_t)xpar * a.world * D;
+      const unsigned down_target = epoch1 * gridDim.x * (unsigned)a.world;
       const float x_inverse = sh.x_inverse;
       const bool tracer = (ct == 0);
       if (tracer) INK_TRACE(layer, kTrLayerStart);
@@ -584,7 +625,12 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
       if (ct == 0) {
         if (plan.n_sg == 0) red_release_add(sync + kShGuDone, 1u);
         if (plan.n_q == 0) red_release_add(sync + kRtGuDone, 1u);
-        if (plan.n_sd + plan.n_qd == 0) red_release_add(sync + kDownDone, 1u);
+        if (plan.n_sd + plan.n_qd == 0) {
+          if (a.world > 1)
+            for (int r = 0; r < a.world; ++r) red_release_sys_add(a.peer_xsync[r] + layer, 1u);
+          else
+            red_release_add(a.xsync + layer, 1u);
+        }
       }
       // ------------------------------------------------ router rows
       for (int t = first_of(plan.s_r); t < plan.s_sg; t += kSC) {
@@ -608,7 +654,7 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
               a.scores[(size_t)par * a.experts + row] = round_bf16(1.f / (1.f + __expf(-l))) + router_bias[row];
             __threadfence();
             const unsigned done = atomicAdd(sync + kRouterRows, 1u) + 1u;
-            if (done == (unsigned)total_rows) sh.tail_request = layer + 1;
+            if (done == epoch1 * (unsigned)total_rows) sh.tail_request = layer + 1;
           }
         } else {
           release(slot);
@@ -714,8 +760,8 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
       consumer_sync();
       // ------------------------------------------------ shared down
       if (lane == 0) {
-        wait_global(sync + kShGuDone, gridDim.x, &sh);
-        wait_global(sync + kRouteReady, 1u, &sh);
+        wait_global(sync + kShGuDone, epoch1 * gridDim.x, &sh);
+        wait_global(sync + kRouteReady, epoch1, &sh);
       }
       __syncwarp();
       if (tracer) INK_TRACE(layer, kTrShGuAll);
@@ -760,7 +806,7 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
       }
       if (tracer) INK_TRACE(layer, kTrShDownDone);
       // ------------------------------------------------ routed down
-      if (lane == 0) wait_global(sync + kRtGuDone, gridDim.x, &sh);
+      if (lane == 0) wait_global(sync + kRtGuDone, epoch1 * gridDim.x, &sh);
       __syncwarp();
       if (tracer) INK_TRACE(layer, kTrRtGuAll);
       if (!sh.failed) {
@@ -847,24 +893,45 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
         // the last tile is always a routed one.)
         if (last_of_block && !sh.failed) {
           __syncwarp();
+          // deliver this block's rows to every rank (itself included), then count the block there
           for (int row = lane; row < plan.n_g * S::RT; row += 32) {
             float total = 0.f;
             for (int j = 0; j < n_jobs; ++j) total += sh.contrib[j][row];
-            a.partial[(size_t)plan.g0 * S::RT + row] = total;
+            const size_t at = ((size_t)xpar * a.world + a.rank) * D + (size_t)plan.g0 * S::RT + row;
+            for (int r = 0; r < a.world; ++r) a.peer_inbox[r][at] = total;
           }
           __syncwarp();
           if (lane == 0) {
-            __threadfence();
-            red_release_add(sync + kDownDone, 1u);
+            if (a.world > 1) {
+              __threadfence_system();
+              for (int r = 0; r < a.world; ++r) red_release_sys_add(a.peer_xsync[r] + layer, 1u);
+            } else {
+              __threadfence();
+              red_release_add(a.xsync + layer, 1u);
+            }
           }
         }
       }
       if (tracer) INK_TRACE(layer, kTrRtDownDone);
-      if (!a.glue) break;
-      // ------------------------------------------------ residual add + RMS norm (every block, redundantly)
-      if (lane == 0) wait_global(sync + kDownDone, gridDim.x, &sh);
+      // every block of every rank has delivered this layer's rows
+      if (lane == 0) {
+        if (a.world > 1) wait_system(a.xsync + layer, down_target, &sh);
+        else wait_global(a.xsync + layer, down_target, &sh);
+      }
       __syncwarp();
       if (tracer) INK_TRACE(layer, kTrDownAll);
+      if (!a.glue) {
+        // one block only: each block writes the sum over the ranks of its own rows
+        if (!sh.failed)
+          for (int row = ct; row < plan.n_g * S::RT; row += kSC * 32) {
+            const size_t i = (size_t)plan.g0 * S::RT + row;
+            float total = 0.f;
+            for (int r = 0; r < a.world; ++r) total += __ldcg(inbox + (size_t)r * D + i);
+            a.partial[i] = total;
+          }
+        break;
+      }
+      // ------------------------------------------------ residual add + RMS norm (every block, redundantly)
       float value[PER];
       {
         const uint16_t* res_in = a.residual + (size_t)par * D;
@@ -872,6 +939,7 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
         float sumsq = 0.f, amax_h = 0.f, amax_w = 0.f;
         // all loads first (they are independent), arithmetic after: one L2 round trip, not PER
         const bool live = !sh.failed;
+        const int world = a.world;
         uint16_t res[PER], nw[PER];
         float part[PER];
 #pragma unroll
@@ -879,7 +947,15 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
           const int i = ct + n * (kSC * 32);
           const bool ok = live && i < D;
           res[n] = ok ? __ldcg(res_in + i) : (uint16_t)0;
-          part[n] = ok ? __ldcg(a.partial + i) : 0.f;
+          // every rank's delivery, summed in rank order (same bits on every rank); predicated loads of a
+          // fixed trip count so that they all issue before the first add
+          float got[kSMaxWorld];
+#pragma unroll
+          for (int r = 0; r < kSMaxWorld; ++r) got[r] = (ok && r < world) ? __ldcg(inbox + (size_t)r * D + i) : 0.f;
+          float sum = 0.f;
+#pragma unroll
+          for (int r = 0; r < kSMaxWorld; ++r) sum += got[r];
+          part[n] = sum;
           nw[n] = ok ? norm_weight[i] : (uint16_t)0;
         }
 #pragma unroll
@@ -890,7 +966,10 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
           sumsq = fmaf(h, h, sumsq);
           amax_h = fmaxf(amax_h, fabsf(h));
           amax_w = fmaxf(amax_w, fabsf(bf16_to_f32(nw[n])));
-          if (blockIdx.x == 0 && live && i < D) res_out[i] = (uint16_t)f32_to_bf16_bits(h);
+          if (blockIdx.x == 0 && live && i < D) {
+            res_out[i] = (uint16_t)f32_to_bf16_bits(h);
+            if (layer + 1 == a.n_layers) a.partial[i] = part[n];
+          }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
@@ -939,6 +1018,9 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
   }
   __syncthreads();
   if (threadIdx.x == 0 && sh.failed && a.status) atomicOr(a.status, kFlagWaitTimedOut);
+  // Every block read the epoch before it could pass any counter, and block 0 gets here only after
+  // the last counter of the launch, so this store cannot be seen by a block of the same launch.
+  if (threadIdx.x == 0 && blockIdx.x == 0) *a.epoch = sh.epoch1;
 }
 
 // ------------------------------------------------------------------- host side
@@ -964,11 +1046,9 @@ static int launch_stack(const StackArgs& a, cudaStream_t stream) {
   const int groups = D / S::RT;
   const int rows_per_block = ((groups + sms - 1) / sms) * S::RT;
   INK_REQUIRE(rows_per_block <= kSMaxRows, kUnsupportedShape, "moe_stack: %d output rows per block", rows_per_block);
-  cudaError_t e = cudaMemsetAsync(a.sync, 0, sizeof(unsigned) * kSyncWordsPerLayer * (size_t)a.n_layers, stream);
-  INK_REQUIRE(e == cudaSuccess, kLaunchFailed, "moe_stack: memset failed: %s", cudaGetErrorString(e));
   StackArgs args = a;
   void* params[] = {&args};
-  e = cudaLaunchCooperativeKernel((const void*)moe_stack_kernel<D, F>, dim3(sms), dim3(kSThreads), params,
+  cudaError_t e = cudaLaunchCooperativeKernel((const void*)moe_stack_kernel<D, F>, dim3(sms), dim3(kSThreads), params,
                                   (size_t)S::SMEM, stream);
   INK_REQUIRE(e == cudaSuccess, kLaunchFailed, "moe_stack: launch failed: %s", cudaGetErrorString(e));
   return kOk;
@@ -980,31 +1060,39 @@ using namespace ink;
 
 extern "C" size_t ink_moe_stack_layer_bytes(void) { return sizeof(StackLayer); }
 
+static size_t pad256(size_t n) { return (n + 255) / 256 * 256; }
+
+// The region other ranks write into: delivered-block counters, then the delivered rows.
+extern "C" size_t ink_moe_stack_symmetric_bytes(int n_layers, int hidden, int world) {
+  return pad256(sizeof(unsigned) * (size_t)n_layers) + pad256(sizeof(float) * 2 * (size_t)world * hidden);
+}
+
 extern "C" size_t ink_moe_stack_scratch_bytes(int n_layers, int hidden, int intermediate, int experts, int n_shared,
                                               int top_k) {
   size_t bytes = 0;
-  auto add = [&](size_t n) { bytes += (n + 255) / 256 * 256; };
-  add(sizeof(unsigned) * kSyncWordsPerLayer * (size_t)n_layers);   // sync
-  add(sizeof(RouteTable) * (size_t)n_layers);                       // routes
-  add(sizeof(float) * 2 * (size_t)(experts + n_shared));            // logits
-  add(sizeof(float) * 2 * (size_t)experts);                         // scores
-  add(2 * 2 * (size_t)top_k * intermediate);                        // activated
-  add(2 * 2 * (size_t)n_shared * intermediate);                     // shared activated
-  add(2 * 2 * (size_t)hidden);                                      // residual double buffer
-  add(sizeof(unsigned long long) * (size_t)n_layers * kTraceBlocks * kTraceSlots);   // phase stamps (tracing)
+  bytes += pad256(sizeof(unsigned) * kSyncWordsPerLayer * (size_t)n_layers);   // sync
+  bytes += pad256(sizeof(unsigned));                                            // epoch
+  bytes += pad256(sizeof(RouteTable) * (size_t)n_layers);                       // routes
+  bytes += pad256(sizeof(float) * 2 * (size_t)(experts + n_shared));            // logits
+  bytes += pad256(sizeof(float) * 2 * (size_t)experts);                         // scores
+  bytes += pad256(2 * 2 * (size_t)top_k * intermediate);                        // activated
+  bytes += pad256(2 * 2 * (size_t)n_shared * intermediate);                     // shared activated
+  bytes += pad256(2 * 2 * (size_t)hidden);                                      // residual double buffer
+  bytes += ink_moe_stack_symmetric_bytes(n_layers, hidden, 1);                  // deliveries when there is one rank
+  bytes += pad256(sizeof(unsigned long long) * (size_t)n_layers * kTraceBlocks * kTraceSlots);   // phase stamps (tracing)
   return bytes;
 }
 
 extern "C" size_t ink_moe_stack_trace_offset(int n_layers, int hidden, int intermediate, int experts,
                                              int n_shared, int top_k) {
   return ink_moe_stack_scratch_bytes(n_layers, hidden, intermediate, experts, n_shared, top_k) -
-         (sizeof(unsigned long long) * (size_t)n_layers * kTraceBlocks * kTraceSlots + 255) / 256 * 256;
+         pad256(sizeof(unsigned long long) * (size_t)n_layers * kTraceBlocks * kTraceSlots);
 }
 
-extern "C" int ink_moe_stack_decode(const void* layers, int n_layers, const void* x, void* residual_io,
-                                    void* normed_out, float* partial_out, int glue, float eps, int hidden,
-                                    int intermediate, int experts, int n_shared, int top_k, void* scratch,
-                                    size_t scratch_bytes, int32_t* status, ink_stream_t stream) {
+static int stack_decode(const void* layers, int n_layers, const void* x, void* residual_io, void* normed_out,
+                        float* partial_out, int glue, float eps, int hidden, int intermediate, int experts,
+                        int n_shared, int top_k, void* scratch, size_t scratch_bytes, int rank, int world,
+                        const uint64_t* peer_regions, int32_t* status, ink_stream_t stream) {
   INK_REQUIRE(layers && x && partial_out && scratch, kBadArgument, "moe_stack: null pointer argument");
   INK_REQUIRE(n_layers >= 1 && (glue == 0 || glue == 1), kBadArgument, "moe_stack: n_layers=%d glue=%d", n_layers, glue);
   INK_REQUIRE(glue || n_layers == 1, kBadArgument, "moe_stack: without the glue only one block can run");
@@ -1012,6 +1100,8 @@ extern "C" int ink_moe_stack_decode(const void* layers, int n_layers, const void
   INK_REQUIRE(top_k >= 1 && top_k <= kSMaxTopK && n_shared >= 0 && n_shared <= kSMaxShared && experts >= top_k &&
                   experts <= kSMaxExperts && top_k + n_shared <= 32,
               kUnsupportedShape, "moe_stack: experts=%d top_k=%d n_shared=%d unsupported", experts, top_k, n_shared);
+  INK_REQUIRE(world >= 1 && world <= kSMaxWorld && rank >= 0 && rank < world && (world == 1 || peer_regions), kBadArgument,
+              "moe_stack: rank=%d world=%d", rank, world);
   INK_REQUIRE(scratch_bytes >= ink_moe_stack_scratch_bytes(n_layers, hidden, intermediate, experts, n_shared, top_k),
               kBadArgument, "moe_stack: scratch of %zu bytes is too small", scratch_bytes);
   INK_REQUIRE(aligned16(x) && aligned16(scratch) && aligned16(partial_out), kMisaligned, "moe_stack: misaligned buffer");
@@ -1027,15 +1117,32 @@ extern "C" int ink_moe_stack_decode(const void* layers, int n_layers, const void
   a.normed_out = (uint16_t*)normed_out;
   a.partial = partial_out;
   a.status = status;
+  a.rank = rank;
+  a.world = world;
   char* p = (char*)scratch;
-  auto take = [&](size_t n) { char* q = p; p += (n + 255) / 256 * 256; return q; };
+  auto take = [&](size_t n) { char* q = p; p += pad256(n); return q; };
   a.sync = (unsigned*)take(sizeof(unsigned) * kSyncWordsPerLayer * (size_t)n_layers);
+  a.epoch = (unsigned*)take(sizeof(unsigned));
   a.routes = (RouteTable*)take(sizeof(RouteTable) * (size_t)n_layers);
   a.logits = (float*)take(sizeof(float) * 2 * (size_t)(experts + n_shared));
   a.scores = (float*)take(sizeof(float) * 2 * (size_t)experts);
   a.activated = (uint16_t*)take(2 * 2 * (size_t)top_k * intermediate);
   a.shared_activated = (uint16_t*)take(2 * 2 * (size_t)n_shared * intermediate);
   a.residual = (uint16_t*)take(2 * 2 * (size_t)hidden);
+  char* own_region = take(ink_moe_stack_symmetric_bytes(n_layers, hidden, 1));
+  for (int r = 0; r < kSMaxWorld; ++r) {
+    a.peer_inbox[r] = nullptr;
+    a.peer_xsync[r] = nullptr;
+  }
+  const size_t counters = pad256(sizeof(unsigned) * (size_t)n_layers);
+  for (int r = 0; r < world; ++r) {
+    char* region = world == 1 ? own_region : (char*)(uintptr_t)peer_regions[r];
+    INK_REQUIRE(region != nullptr && aligned16(region), kBadArgument, "moe_stack: bad region for rank %d", r);
+    a.peer_xsync[r] = (unsigned*)region;
+    a.peer_inbox[r] = (float*)(region + counters);
+  }
+  a.xsync = a.peer_xsync[rank];
+  a.inbox = a.peer_inbox[rank];
   // INKLING_STACK_TRACE=1: blocks stamp their phase boundaries (global nanosecond timer) into the
   // tail of the scratch, where ink_moe_stack_trace_offset() says
   const char* tracing = getenv("INKLING_STACK_TRACE");
@@ -1068,4 +1175,21 @@ extern "C" int ink_moe_stack_decode(const void* layers, int n_layers, const void
     INK_REQUIRE(e == cudaSuccess, kLaunchFailed, "moe_stack: copy failed: %s", cudaGetErrorString(e));
   }
   return kOk;
+}
+
+extern "C" int ink_moe_stack_decode(const void* layers, int n_layers, const void* x, void* residual_io,
+                                    void* normed_out, float* partial_out, int glue, float eps, int hidden,
+                                    int intermediate, int experts, int n_shared, int top_k, void* scratch,
+                                    size_t scratch_bytes, int32_t* status, ink_stream_t stream) {
+  return stack_decode(layers, n_layers, x, residual_io, normed_out, partial_out, glue, eps, hidden, intermediate,
+                      experts, n_shared, top_k, scratch, scratch_bytes, 0, 1, nullptr, status, stream);
+}
+
+extern "C" int ink_moe_stack_decode_tp(const void* layers, int n_layers, const void* x, void* residual_io,
+                                       void* normed_out, float* partial_out, int glue, float eps, int hidden,
+                                       int intermediate, int experts, int n_shared, int top_k, void* scratch,
+                                       size_t scratch_bytes, int rank, int world, const uint64_t* peer_regions,
+                                       int32_t* status, ink_stream_t stream) {
+  return stack_decode(layers, n_layers, x, residual_io, normed_out, partial_out, glue, eps, hidden, intermediate,
+                      experts, n_shared, top_k, scratch, scratch_bytes, rank, world, peer_regions, status, stream);
 }

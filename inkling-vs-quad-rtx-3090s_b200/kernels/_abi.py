@@ -37,6 +37,8 @@ _SIGNATURES = {
     "ink_moe_stack_scratch_bytes": (Z, [I, I, I, I, I, I]),
     "ink_moe_stack_trace_offset": (Z, [I, I, I, I, I, I]),
     "ink_moe_stack_decode": (I, [P, I, P, P, P, P, I, F, I, I, I, I, I, P, Z, P, P]),
+    "ink_moe_stack_symmetric_bytes": (Z, [I, I, I]),
+    "ink_moe_stack_decode_tp": (I, [P, I, P, P, P, P, I, F, I, I, I, I, I, P, Z, I, I, P, P, P]),
 }
 
 

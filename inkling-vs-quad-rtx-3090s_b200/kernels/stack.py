@@ -20,7 +20,7 @@ class StackDescriptor:
     """Device-side table of block descriptors plus the kernel's scratch; built once."""
 
     def __init__(self, blocks: list[dict], hidden: int, intermediate: int, experts: int, n_shared: int,
-                 top_k: int, device):
+                 top_k: int, device, group=None):
         assert struct.calcsize(_LAYER_FORMAT) == _abi.lib().ink_moe_stack_layer_bytes()
         self.keep = blocks   # the tensors the addresses point into
         self.n_layers, self.hidden, self.intermediate = len(blocks), hidden, intermediate
@@ -33,8 +33,29 @@ class StackDescriptor:
             for b in blocks)
         self.table = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(device)
         size = _abi.lib().ink_moe_stack_scratch_bytes(self.n_layers, hidden, intermediate, experts, n_shared, top_k)
-        self.scratch = torch.zeros(size, dtype=torch.uint8, device=device)
+        self.scratch = torch.zeros(size, dtype=torch.uint8, device=device)   # counters start at zero, then only grow
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.rank, self.world, self.peer_regions, self.symmetric = 0, 1, None, None
+        if group is not None and torch.distributed.is_initialized() and torch.distributed.get_world_size(group) > 1:
+            self._join(group, device)
+
+    def _join(self, group, device) -> None:
+        """Tensor-parallel ranks: one symmetric buffer per rank that every rank can store into
+        (torch symmetric memory does the peer mapping; this is plumbing, the kernel does the rest)."""
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.rank = torch.distributed.get_rank(group)
+        self.world = torch.distributed.get_world_size(group)
+        size = _abi.lib().ink_moe_stack_symmetric_bytes(self.n_layers, self.hidden, self.world)
+        self.symmetric = symm_mem.empty(size, dtype=torch.uint8, device=device)
+        self.symmetric.zero_()
+        handle = symm_mem.rendezvous(self.symmetric, group)
+        self._handle = handle
+        self.peer_regions = (ctypes.c_uint64 * self.world)(*[int(p) for p in handle.buffer_ptrs])
+        torch.cuda.synchronize()
+        torch.distributed.barrier(group)   # every rank's region is zero before anyone delivers into it
 
     def decode(self, x, partial_out, residual_io=None, normed_out=None, eps: float = 1e-6) -> None:
         glue = residual_io is not None
@@ -44,17 +65,23 @@ class StackDescriptor:
             assert residual_io.dtype == normed_out.dtype == torch.bfloat16
             assert residual_io.numel() == normed_out.numel() == self.hidden
         _abi.require_cuda(x, partial_out, residual_io, normed_out)
-        _abi.check(_abi.lib().ink_moe_stack_decode(
-            self.table.data_ptr(), self.n_layers, x.data_ptr(), _abi.ptr(residual_io), _abi.ptr(normed_out),
-            partial_out.data_ptr(), int(glue), float(eps), self.hidden, self.intermediate, self.experts,
-            self.n_shared, self.top_k, self.scratch.data_ptr(), self.scratch.numel(), self.status.data_ptr(),
-            _abi.stream()))
+        common = (self.table.data_ptr(), self.n_layers, x.data_ptr(), _abi.ptr(residual_io), _abi.ptr(normed_out),
+                  partial_out.data_ptr(), int(glue), float(eps), self.hidden, self.intermediate, self.experts,
+                  self.n_shared, self.top_k, self.scratch.data_ptr(), self.scratch.numel())
+        if self.world == 1:
+            _abi.check(_abi.lib().ink_moe_stack_decode(*common, self.status.data_ptr(), _abi.stream()))
+        else:
+            _abi.check(_abi.lib().ink_moe_stack_decode_tp(*common, self.rank, self.world, self.peer_regions,
+                                                          self.status.data_ptr(), _abi.stream()))
 
     def check_status(self) -> None:
         """Host read (synchronises): raises if a bounded wait inside the kernel gave up."""
         flags = int(self.status.item())
         self.status.zero_()
         if flags & 2:
+            self.scratch.zero_()   # the counters are inconsistent after an abandoned launch
+            if self.symmetric is not None:
+                self.symmetric.zero_()
             raise RuntimeError("moe_stack: a bounded wait inside the kernel timed out; the output is invalid")
 
     TRACE_SLOTS = ("layer_start", "router_rows_done", "shared_gate_up_done", "routed_gate_up_done",

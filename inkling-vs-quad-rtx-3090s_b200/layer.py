@@ -175,14 +175,18 @@ class FusedMoE(nn.Module):
                     shared_down=self.shared_down, norm_weight=norm_weight, topk_indices=self.topk_indices,
                     topk_weights=self.topk_weights, gammas=self.gammas, route_scale=self.route_scale)
 
-    def one_launch_supported(self) -> bool:
-        ex = self.experts
-        world = 1
+    def world_size(self) -> int:
         group = _group_of(self.device_mesh)
-        if group is not None and torch.distributed.is_initialized():
-            world = torch.distributed.get_world_size(group)
-        return (world == 1 and ex.start == 0 and
-                stack_supported(ex.hidden_dim, ex.intermediate_dim, ex.local, self.n_shared, self.top_k))
+        if group is not None and torch.distributed.is_available() and torch.distributed.is_initialized():
+            return torch.distributed.get_world_size(group)
+        return 1
+
+    def one_launch_supported(self) -> bool:
+        """One token through this block in one persistent launch (the all-reduce, if any,
+        follows as its own collective)."""
+        ex = self.experts
+        return ex.start == 0 and stack_supported(ex.hidden_dim, ex.intermediate_dim, ex.local, self.n_shared,
+                                                 self.top_k)
 
     def _reserve(self, tokens: int) -> None:
         if tokens <= self._tokens:
@@ -235,8 +239,10 @@ class FusedMoE(nn.Module):
         ex = self.experts
         if t == 1 and self.one_launch_supported():
             if self._fused is None:
+                # across ranks the kernel delivers and sums the partials itself: no separate collective
                 self._fused = StackDescriptor([self.block_descriptor()], ex.hidden_dim, ex.intermediate_dim,
-                                              ex.local, self.n_shared, self.top_k, flat.device)
+                                              ex.local, self.n_shared, self.top_k, flat.device,
+                                              group=_group_of(self.device_mesh))
             self._fused.decode(flat, self.partial[:1])
             return self.partial[:1]
         self.route(flat)

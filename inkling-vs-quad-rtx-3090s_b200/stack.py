@@ -21,6 +21,7 @@ class MoEStack(nn.Module):
         self.norm_weight = torch.ones(hidden, dtype=torch.bfloat16, device=dev)
         self._tokens = 0
         self._fused = None
+        # one launch for the whole stack, on one GPU or across tensor-parallel ranks
         self.one_launch = all(layer.one_launch_supported() for layer in layers)
 
     @classmethod
@@ -57,8 +58,9 @@ class MoEStack(nn.Module):
                 first = self.layers[0]
                 ex = first.experts
                 blocks = [layer.block_descriptor(self.norm_weight) for layer in self.layers]
+                from .layer import _group_of
                 self._fused = StackDescriptor(blocks, ex.hidden_dim, ex.intermediate_dim, ex.local, first.n_shared,
-                                              first.top_k, x.device)
+                                              first.top_k, x.device, group=_group_of(first.device_mesh))
                 self._fused_generations = tuple(layer.generation for layer in self.layers)
             self._fused.decode(x, self.layers[-1].partial[:1], residual, normed, self.eps)
             return normed
