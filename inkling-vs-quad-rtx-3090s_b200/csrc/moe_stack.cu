@@ -210,7 +210,7 @@ struct StackShared {
   float x_inverse;                      // inverse normaliser of the staged x
   int done[2][3];                       // tiles finished per layer parity: shared g/u, routed g/u, down
   unsigned epoch1;                      // launches completed before this one, plus one: scales every target
-  volatile int tail_request;            // layer + 1 whose router tail this block must run
+  volatile int routed_layers;           // layers whose routing table is in `routes` (set by the auxiliary warp)
   volatile int failed;
 };
 
@@ -267,6 +267,25 @@ __device__ __forceinline__ bool wait_system(const unsigned* p, unsigned target, 
   return true;
 }
 
+// Bounded wait until this block's auxiliary warp has resolved the routing of `layer`.
+__device__ __forceinline__ bool wait_routing(int layer, StackShared* sh) {
+  if (sh->failed) return false;
+  if (sh->routed_layers > layer) {
+    __threadfence_block();
+    return true;
+  }
+  const long long t0 = clock64();
+  while (sh->routed_layers <= layer) {
+    if (sh->failed) return false;
+    if (clock64() - t0 > kWaitLimitCycles) {
+      sh->failed = 1;
+      return false;
+    }
+  }
+  __threadfence_block();
+  return true;
+}
+
 __device__ __forceinline__ void consumer_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(kSC * 32) : "memory");
 }
@@ -274,7 +293,6 @@ __device__ __forceinline__ void consumer_sync() {
 // -------------------------------------------------------------------- router tail
 // One warp. logits/scores of the layer are complete in global memory.
 __device__ void stack_router_tail(const StackArgs& a, const StackLayer& ly, int layer, StackShared* sh) {
-  const unsigned epoch1 = sh->epoch1;
   const int lane = threadIdx.x & 31;
   const int par = layer & 1;
   const float* logit = a.logits + (size_t)par * (a.experts + a.n_shared);
@@ -327,7 +345,8 @@ __device__ void stack_router_tail(const StackArgs& a, const StackLayer& ly, int 
   float w = round_bf16(__expf(round_bf16(lp - lse)));
   w = round_bf16(w * ly.route_scale);
   w = round_bf16(w * bf16_to_f32(ly.global_scale[0]));
-  RouteTable* table = a.routes + layer;
+  RouteTable* table = &sh->routes[layer & 1];
+  const bool publish = blockIdx.x == 0;   // one block also writes the optional router outputs
   if (lane < a.top_k) {
     const int64_t* entry = ly.sources + (size_t)my_choice * kBank;
     RouteEntry r;
@@ -340,16 +359,16 @@ __device__ void stack_router_tail(const StackArgs& a, const StackLayer& ly, int 
     r.weight = w;
     r.expert = my_choice;
     table->route[lane] = r;
-    if (ly.topk_indices) ly.topk_indices[lane] = my_choice;
-    if (ly.topk_weights) ly.topk_weights[lane] = (uint16_t)f32_to_bf16_bits(w);
+    if (publish && ly.topk_indices) ly.topk_indices[lane] = my_choice;
+    if (publish && ly.topk_weights) ly.topk_weights[lane] = (uint16_t)f32_to_bf16_bits(w);
   } else if (live) {
     table->gamma[lane - a.top_k] = w;
-    if (ly.gammas) ly.gammas[lane - a.top_k] = (uint16_t)f32_to_bf16_bits(w);
+    if (publish && ly.gammas) ly.gammas[lane - a.top_k] = (uint16_t)f32_to_bf16_bits(w);
   }
   __syncwarp();
   if (lane == 0) {
-    __threadfence();
-    st_release_u32(a.sync + (size_t)layer * kSyncWordsPerLayer + kRouteReady, epoch1);
+    __threadfence_block();
+    sh->routed_layers = layer + 1;   // the producer and the consumers of this block may read the table
   }
 }
 
@@ -397,7 +416,7 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
       mbar_init(&sh.full[s], 1);
       mbar_init(&sh.empty[s], 1);
     }
-    sh.tail_request = 0;
+    sh.routed_layers = 0;
     sh.failed = 0;
     sh.epoch1 = *a.epoch + 1u;
     for (int i = 0; i < 6; ++i) (&sh.done[0][0])[i] = 0;
@@ -463,14 +482,8 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
         if (!alive) break;
         // ---- routing of this layer: wait, then bring the table into shared memory
         INK_TRACE(layer, kTrProdRouteWait);
-        if (!wait_global(sync + kRouteReady, sh.epoch1, &sh)) break;
+        if (!wait_routing(layer, &sh)) break;
         INK_TRACE(layer, kTrProdRouteGot);
-        {
-          const uint4* src = reinterpret_cast<const uint4*>(a.routes + layer);
-          uint4* tab = reinterpret_cast<uint4*>(&sh.routes[layer & 1]);
-#pragma unroll
-          for (int i = 0; i < (int)(sizeof(RouteTable) / 16); ++i) tab[i] = __ldcg(src + i);
-        }
         const RouteTable& table = sh.routes[layer & 1];
         // ---- routed gate/up
         {
@@ -528,23 +541,13 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
     // =========================================================== auxiliary warp
     for (int layer = 0; layer < a.n_layers; ++layer) {
       const unsigned* sync = a.sync + (size_t)layer * kSyncWordsPerLayer;
-      const long long t0 = clock64();
-      for (;;) {
-        if (sh.tail_request == layer + 1) {
-          __threadfence();
-          stack_router_tail(a, a.layers[layer], layer, &sh);
-          break;
-        }
-        unsigned ready = 0;
-        if (lane == 0) ready = ld_acquire_u32(sync + kRouteReady) >= sh.epoch1;
-        ready = __shfl_sync(0xffffffffu, ready, 0);
-        if (ready || sh.failed) break;
-        if (clock64() - t0 > 4 * kWaitLimitCycles) {
-          sh.failed = 1;
-          break;
-        }
-        __nanosleep(200);
-      }
+      // every block resolves the routing for itself (same inputs, same arithmetic, same result): the
+      // code stays warm in this SM's instruction cache and nothing has to be published between blocks
+      bool ok = true;
+      if (lane == 0) ok = wait_global(sync + kRouterRows, sh.epoch1 * (unsigned)(a.experts + a.n_shared), &sh);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      stack_router_tail(a, a.layers[layer], layer, &sh);
       if (sh.failed) break;
     }
   } else {
@@ -654,7 +657,7 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
               a.scores[(size_t)par * a.experts + row] = round_bf16(1.f / (1.f + __expf(-l))) + router_bias[row];
             __threadfence();
             const unsigned done = atomicAdd(sync + kRouterRows, 1u) + 1u;
-            if (done == epoch1 * (unsigned)total_rows) sh.tail_request = layer + 1;
+            (void)done;
           }
         } else {
           release(slot);
@@ -761,14 +764,14 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
       // ------------------------------------------------ shared down
       if (lane == 0) {
         wait_global(sync + kShGuDone, epoch1 * gridDim.x, &sh);
-        wait_global(sync + kRouteReady, epoch1, &sh);
+        wait_routing(layer, &sh);
       }
       __syncwarp();
       if (tracer) INK_TRACE(layer, kTrShGuAll);
       if (!sh.failed) {
         for (int e = cw; e < a.n_shared; e += kSC) {
           const uint16_t* src = a.shared_activated + ((size_t)par * a.n_shared + e) * F;
-          const float gamma = __ldcg(&a.routes[layer].gamma[e]);
+          const float gamma = sh.routes[par].gamma[e];
           uint32_t* dst = reinterpret_cast<uint32_t*>(s_sact + (size_t)e * F);
           for (int i = lane; i < F / 2; i += 32) {
             const uint32_t v = __ldcg(reinterpret_cast<const uint32_t*>(src) + i);

@@ -17,10 +17,19 @@ __device__ __forceinline__ float dot32(const uint4& q, uint32_t scale_pair, cons
   a1 = hfma2(h[0], x[8], a1); a1 = hfma2(h[1], x[9], a1); a1 = hfma2(h[2], x[10], a1); a1 = hfma2(h[3], x[11], a1);
   e2m1x8_to_f16x2(q.w, h);
   a1 = hfma2(h[0], x[12], a1); a1 = hfma2(h[1], x[13], a1); a1 = hfma2(h[2], x[14], a1); a1 = hfma2(h[3], x[15], a1);
+  // The conversion unit is the scarce resource of this loop (the E2M1 converts above saturate it), so
+  // the two block sums are added in FP16 (b = (a0.lo + a0.hi, a1.lo + a1.hi)) and multiplied by their
+  // E4M3 scales with FP32-accumulating mixed-precision FMAs instead of being converted to FP32 first.
   const uint32_t s = e4m3x2_to_f16x2((uint16_t)scale_pair);
-  const float b0 = f16lo_to_f32(a0) + f16hi_to_f32(a0);
-  const float b1 = f16lo_to_f32(a1) + f16hi_to_f32(a1);
-  return fmaf(f16lo_to_f32(s), b0, f16hi_to_f32(s) * b1);
+  const uint32_t lows = __byte_perm(a0, a1, 0x5410), highs = __byte_perm(a0, a1, 0x7632);
+  uint32_t b;
+  asm("add.rn.f16x2 %0, %1, %2;" : "=r"(b) : "r"(lows), "r"(highs));
+  float acc = 0.f;
+  asm("{\n .reg .b16 s0, s1, b0, b1;\n mov.b32 {s0, s1}, %1;\n mov.b32 {b0, b1}, %2;\n"
+      " fma.rn.f32.f16 %0, s0, b0, %0;\n fma.rn.f32.f16 %0, s1, b1, %0;\n}\n"
+      : "+f"(acc)
+      : "r"(s), "r"(b));
+  return acc;
 }
 
 // 8 BF16 weights x 8 BF16 activations, FP32 accumulate
