@@ -26,7 +26,7 @@
 
 namespace ink {
 
-constexpr int kSC = 10;                                // consumer warps
+constexpr int kSC = 8;                                 // consumer warps
 constexpr int kSStages = 2 * kSC;                      // ring slots
 constexpr int kSSlot = 9216;                           // bytes per slot
 constexpr int kSThreads = (kSC + 2) * 32;              // producer + consumers + auxiliary
@@ -642,7 +642,7 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
         if (!take(t, src, slot)) break;
         if (t < plan.n_r) {
           float acc = 0.f;
-#pragma unroll
+#pragma unroll 2
           for (int c = 0; c < S::R_CPL; ++c) {
             const int chunk = c * 32 + lane;
             acc = dot8(*reinterpret_cast<const uint4*>(src + chunk * 16), reinterpret_cast<const uint4*>(s_xbf)[chunk], acc);
@@ -680,9 +680,11 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
               for (int p = 0; p < S::SG_PAIRS; ++p) g[p] = u[p] = 0.f;
             }
             const uint4* xs = reinterpret_cast<const uint4*>(s_xbf + h * S::SG_COLS);
+            // short loop bodies on purpose: straight-line code as long as a tile does not fit the
+            // instruction cache close to the schedulers, and fetching it becomes the bottleneck
 #pragma unroll
             for (int p = 0; p < S::SG_PAIRS; ++p) {
-#pragma unroll
+#pragma unroll 2
               for (int c = 0; c < S::SG_CPL; ++c) {
                 const int chunk = c * 32 + lane;
                 const uint4 xv = xs[chunk];
@@ -730,28 +732,22 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
           const int choice = q / per_job, row0 = (q % per_job) * S::QG_ROWS;
           const RouteEntry r = sh.routes[par].route[choice];
           if (r.gu_codes) {
-            float g[S::QG_PAIRS], u[S::QG_PAIRS];
+            const float scale = r.gu_scale2 * x_inverse;
+            uint16_t* y = a.activated + ((size_t)par * a.top_k + choice) * F + row0 / 2;
+            float gate = 0.f;
+#pragma unroll 1
+            for (int row = 0; row < S::QG_ROWS; ++row) {   // even rows are gate, odd rows up
+              const unsigned char* codes = src + (size_t)row * (D / 2) + lane * 16;
+              const unsigned char* scales = src + S::QG_CODES + (size_t)row * (D / 16) + lane * 2;
+              float acc = 0.f;
 #pragma unroll
-            for (int p = 0; p < S::QG_PAIRS; ++p) {
-              float acc_g = 0.f, acc_u = 0.f;
-#pragma unroll
-              for (int j = 0; j < S::QG_CPL; ++j) {
-                const int chunk = j * 32 + lane;
-                const unsigned char* rg = src + (size_t)(2 * p) * (D / 2) + chunk * 16;
-                const unsigned char* sg = src + S::QG_CODES + (size_t)(2 * p) * (D / 16) + chunk * 2;
-                acc_g += dot32(*reinterpret_cast<const uint4*>(rg), *reinterpret_cast<const uint16_t*>(sg), xr[j]);
-                acc_u += dot32(*reinterpret_cast<const uint4*>(rg + D / 2), *reinterpret_cast<const uint16_t*>(sg + D / 16), xr[j]);
-              }
-              g[p] = acc_g;
-              u[p] = acc_u;
+              for (int j = 0; j < S::QG_CPL; ++j)
+                acc += dot32(*reinterpret_cast<const uint4*>(codes + j * 512), *reinterpret_cast<const uint16_t*>(scales + j * 64), xr[j]);
+              acc = warp_sum(acc) * scale;
+              if ((row & 1) == 0) gate = acc;
+              else if (lane == 0) y[row >> 1] = (uint16_t)f32_to_bf16_bits(silu_mul(gate, acc));
             }
             release(slot);
-            const float scale = r.gu_scale2 * x_inverse;
-            const float gate = multi_reduce<S::QG_PAIRS>(g, lane) * scale;
-            const float up = multi_reduce<S::QG_PAIRS>(u, lane) * scale;
-            if (reduced_owner<S::QG_PAIRS>(lane))
-              a.activated[((size_t)par * a.top_k + choice) * F + row0 / 2 + reduced_row<S::QG_PAIRS>(lane)] =
-                  (uint16_t)f32_to_bf16_bits(silu_mul(gate, up));
           } else {
             release(slot);
           }
@@ -789,21 +785,18 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
         const int e = i / per_e, rem = i % per_e;
         const int local0 = (rem / S::SD_PER_GROUP) * S::RT + (rem % S::SD_PER_GROUP) * S::SD_ROWS;
         const uint4* xs = reinterpret_cast<const uint4*>(s_sact + (size_t)e * F);
-        float r[S::SD_ROWS];
-#pragma unroll
+#pragma unroll 1
         for (int row = 0; row < S::SD_ROWS; ++row) {
           float acc = 0.f;
-#pragma unroll
+#pragma unroll 2
           for (int c = 0; c < S::SD_CPL; ++c) {
             const int chunk = c * 32 + lane;
             acc = dot8(*reinterpret_cast<const uint4*>(src + (size_t)row * F * 2 + chunk * 16), xs[chunk], acc);
           }
-          r[row] = acc;
+          acc = warp_sum(acc);
+          if (lane == 0) sh.contrib[a.top_k + e][local0 + row] = round_bf16(acc);
         }
         release(slot);
-        const float total = multi_reduce<S::SD_ROWS>(r, lane);
-        if (reduced_owner<S::SD_ROWS>(lane))
-          sh.contrib[a.top_k + e][local0 + reduced_row<S::SD_ROWS>(lane)] = round_bf16(total);
         // down tiles are counted together (shared + routed)
         section_done(layer, 2, plan.n_sd + plan.n_qd, false);
       }
@@ -845,8 +838,8 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
                 }
               }
             }
-            float rs[S::PASSES];
-#pragma unroll
+            const float scale = r.dn_scale2 * sh.inverse[choice];
+#pragma unroll 1
             for (int p = 0; p < S::PASSES; ++p) {
               const int row = p * S::RPP + rp;
               float acc = 0.f;
@@ -856,28 +849,14 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
                 acc += dot32(*reinterpret_cast<const uint4*>(src + (size_t)row * (F / 2) + chunk * 16),
                              *reinterpret_cast<const uint16_t*>(src + S::QD_CODES + (size_t)row * (F / 16) + chunk * 2), xr[j]);
               }
-              rs[p] = acc;
+#pragma unroll
+              for (int o = S::LPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+              if (sl == 0) {
+                const float down = round_bf16(acc * scale);
+                sh.contrib[choice][local0 + row] = round_bf16(down * r.weight);
+              }
             }
             release(slot);
-            const float scale = r.dn_scale2 * sh.inverse[choice];
-            if constexpr (S::LPR == 32) {
-              const float total = multi_reduce<S::PASSES>(rs, lane);
-              if (reduced_owner<S::PASSES>(lane)) {
-                const float down = round_bf16(total * scale);
-                sh.contrib[choice][local0 + reduced_row<S::PASSES>(lane)] = round_bf16(down * r.weight);
-              }
-            } else {
-#pragma unroll
-              for (int p = 0; p < S::PASSES; ++p) {
-                float v = rs[p];
-#pragma unroll
-                for (int o = S::LPR / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                if (sl == 0) {
-                  const float down = round_bf16(v * scale);
-                  sh.contrib[choice][local0 + p * S::RPP + rp] = round_bf16(down * r.weight);
-                }
-              }
-            }
           } else {
             release(slot);
           }
