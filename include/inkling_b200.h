@@ -205,7 +205,11 @@ int ink_expert_reduce(const void* down, const int64_t* indices, const void* weig
  *                        const void *global_scale; const int64_t *sources;    (sources: [experts][6])
  *                        const void *shared_gate, *shared_up, *shared_down; const void *norm_weight;
  *                        int64_t *topk_indices; void *topk_weights; void *gammas;    (optional outputs, may be null)
+ *                        const void *bank_maps;   (device copy of ink_moe_stack_encode_banks' 512 bytes, or null)
  *                        float route_scale; int pad; }
+ *               With bank_maps set in every layer the routed experts run on the tensor cores
+ *               (tcgen05.mma kind::mxf4nvf4 on the packed codes and their block scales, no
+ *               conversion); with null in every layer they run on the CUDA cores.
  *  x            BF16 [hidden]: input of the first block
  *  glue = 0     n_layers must be 1; partial_out FP32 [hidden] receives the block's output
  *  glue = 1     residual_io BF16 [hidden] is the residual stream (updated in place),
@@ -219,10 +223,21 @@ int ink_expert_reduce(const void* down, const int64_t* indices, const void* weig
  * experts <= 512, top_k <= 8, n_shared <= 2. The device must support cooperative launches.
  */
 size_t ink_moe_stack_layer_bytes(void);
+/* Encodes, on the host, the four TMA descriptors (4 x 128 bytes) through which the one-launch
+ * kernel streams a layer's NVFP4 banks: gate/up codes [experts][2f][hidden/2], gate/up scales
+ * [experts][2f][hidden/16], down codes [experts][hidden][f/2], down scales [experts][hidden][f/16],
+ * each given by the device address of expert 0 and the byte distance between consecutive experts
+ * (a multiple of 16; the banks of one kind must be evenly spaced, e.g. one allocation). Copy the
+ * 512 bytes to 128-byte aligned device memory and point the layer's bank_maps at them. Has no
+ * counterpart in the reference, which passes per-expert addresses (my_inkling/offloaded_experts.py:41-53). */
+int ink_moe_stack_encode_banks(void* out_host_512, const void* gate_up_codes, uint64_t gate_up_codes_stride,
+                               const void* gate_up_scales, uint64_t gate_up_scales_stride, const void* down_codes,
+                               uint64_t down_codes_stride, const void* down_scales, uint64_t down_scales_stride,
+                               int experts, int hidden, int intermediate);
 /* Tracing (the reference's counterpart is utils/profiling.py:36-78): with the environment
  * variable INKLING_STACK_TRACE=1 every block stamps its phase boundaries with the global
  * nanosecond timer into the scratch at this byte offset, laid out
- * [n_layers][256 blocks][16 slots] of uint64 (slot meanings: enum TraceSlot in moe_stack.cu). */
+ * [n_layers][256 blocks][24 slots] of uint64 (slot meanings: enum TraceSlot in moe_stack.cu). */
 size_t ink_moe_stack_trace_offset(int n_layers, int hidden, int intermediate, int experts, int n_shared,
                                   int top_k);
 size_t ink_moe_stack_scratch_bytes(int n_layers, int hidden, int intermediate, int experts, int n_shared,

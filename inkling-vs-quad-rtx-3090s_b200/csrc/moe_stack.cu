@@ -17,12 +17,14 @@
 // kFlagWaitTimedOut in the status word, marks the launch as failed and every loop
 // drains without further waiting.
 #include <stdlib.h>
+#include <string.h>
 
 #include "../../include/inkling_b200.h"
 #include "common.cuh"
 #include "decode_args.cuh"
 #include "pipe.cuh"
 #include "stream_math.cuh"
+#include "tc_path.cuh"
 
 namespace ink {
 
@@ -30,20 +32,25 @@ constexpr int kSC = 8;                                 // consumer warps
 constexpr int kSStages = 2 * kSC;                      // ring slots
 constexpr int kSSlot = 9216;                           // bytes per slot
 constexpr int kSThreads = (kSC + 2) * 32;              // producer + consumers + auxiliary
+constexpr int kSThreadsTc = (kSC + 2 + 8) * 32;        // tensor-core variant: + 4 warps that write weight scales, 4 that read accumulators
 constexpr int kSMaxTopK = 8;
 constexpr int kSMaxShared = 2;
 constexpr int kSMaxRows = 64;                          // output rows one block may own
 constexpr int kSMaxExperts = 512;
 constexpr int kSyncWordsPerLayer = 8;                  // counters of one layer
 constexpr int kSMaxWorld = 8;                          // tensor-parallel ranks
+constexpr int kTileCountersPerLayer = kSMaxTopK * 32 + 32;   // routed gate/up tiles (at most 8 x 32), then down row tiles
 
 constexpr int kTraceBlocks = 256;
-constexpr int kTraceSlots = 16;
+constexpr int kTraceSlots = 24;
 // phase stamps written by consumer warp 0 (and slot 12..14 by the producer) when tracing is on
 enum TraceSlot {
   kTrLayerStart = 0, kTrRouterDone = 1, kTrShGuDone = 2, kTrRtGuDone = 3, kTrShGuAll = 4, kTrShDownDone = 5,
   kTrRtGuAll = 6, kTrActStaged = 7, kTrRtDownDone = 8, kTrDownAll = 9, kTrNormDone = 10,
   kTrProdRouteWait = 12, kTrProdRouteGot = 13, kTrProdLayerIssued = 14,
+  kTrXDigits = 11, kTrXVisible = 15,                                         // tensor-core variant, consumers
+  kTrMmaGuStart = 16, kTrMmaGuEnd = 17, kTrMmaDownStart = 18, kTrMmaDownEnd = 19,   // the issuing thread
+  kTrScalesGuEnd = 20, kTrScalesDownEnd = 21,                                // first warp that writes weight scales
 };
 __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
@@ -88,6 +95,8 @@ struct StackLayer {
   int64_t* topk_indices;           // [top_k] optional outputs of the router
   uint16_t* topk_weights;          // [top_k]
   uint16_t* gammas;                // [n_shared]
+  const void* tmaps;               // four TMA descriptors of the layer's banks (gate/up codes, gate/up scales, down codes,
+                                   // down scales), or null: the routed experts then run on the CUDA cores
   float route_scale;
   int pad;
 };
@@ -107,6 +116,11 @@ struct StackArgs {
   uint16_t* activated;             // scratch [2][top_k][f]
   uint16_t* shared_activated;      // scratch [2][n_shared][f]
   RouteTable* routes;              // scratch [n_layers]
+  float* gu_part;                  // scratch [top_k * 2f/128 tiles][hidden/256][128]: partial gate/up rows of a tile split between blocks
+  float* dn_part;                  // scratch [top_k * hidden/128 tiles][f/256][128]: the same for the down projection
+  float* sd_out;                   // scratch [2][n_shared][hidden]: shared experts' down rows (tensor-core variant)
+  unsigned* act_amax;              // scratch [2][kSMaxTopK]: largest |activation| bits of each route (tensor-core variant)
+  unsigned* tilesync;              // scratch [n_layers][tile counters]: blocks that have stored their part of a tile (epoch-based)
   unsigned* sync;                  // scratch [n_layers][kSyncWordsPerLayer]: counters that only grow (see epoch)
   unsigned* epoch;                 // scratch: launches completed so far on this rank; every target scales with it
   // tensor-parallel ranks (world == 1: the "peers" are this rank's own scratch)
@@ -152,9 +166,20 @@ struct StackShape {
   static_assert(R_BYTES <= kSSlot && 2 * SG_PART <= kSSlot && QG_CODES + QG_SCALES <= kSSlot, "tile exceeds slot");
   static_assert(QD_CODES + QD_SCALES <= kSSlot && SD_BYTES <= kSSlot, "tile exceeds slot");
   // staging that overlays: [x FP16 | x BF16] during gate/up, [routed act FP16 | shared act BF16] during down
-  static constexpr int STAGING = (kSMaxTopK * F * 2 + kSMaxShared * F * 2) > D * 4
-                                     ? (kSMaxTopK * F * 2 + kSMaxShared * F * 2) : D * 4;
-  static constexpr int SMEM = kSStages * kSSlot + STAGING;
+  // tensor-core path: [x digit rows D*4 | x BF16] during gate/up
+  static constexpr int GU_TILES = 2 * F / kTcRows;          // 128-row tiles per expert
+  static constexpr int GU_CHUNKS = D / kTcChunkK;           // units per tile
+  static constexpr int DN_TILES = D / kTcRows;              // 128-row tiles of the down projection per expert
+  static constexpr int DN_CHUNKS = F / kTcChunkK;
+  static constexpr int STAGING_A = kSMaxTopK * F * 2 + kSMaxShared * F * 2;
+  // tensor-core variant: the shared experts' activations are staged while the digit rows of x are still
+  // being read, so they sit behind both digit-row areas
+  static constexpr int TC_SACT = D * 6 > F * 16 ? D * 6 : F * 16;
+  static constexpr int STAGING_B = TC_SACT + kSMaxShared * F * 2;
+  static constexpr int STAGING = STAGING_A > STAGING_B ? STAGING_A : STAGING_B;
+  static constexpr int SMEM = kSStages * kSSlot + STAGING + 1024;   // the ring starts on a 1024-byte boundary
+  static_assert(2 * kSSlot == kTcUnitBytes, "a tensor-core unit takes exactly two ring slots");
+  static_assert(D % kTcChunkK == 0 && (2 * F) % kTcRows == 0 && D / 64 * 4 <= 512 - kTcColSfb, "shape does not tile");
 };
 
 // The tile list of one block for one layer, identical for every layer.
@@ -166,10 +191,13 @@ struct TilePlan {
   // section starts in the per-layer sequence
   int s_r, s_sg, s_qg, s_sd, s_qd, s_pad, per_layer;
   int n_sg, n_sd, n_qd;   // tiles in the sections (with padding where the section is padded)
+  int qu0, n_qu;          // tensor-core path: routed gate/up units [qu0, qu0 + n_qu) of top_k * GU_TILES * GU_CHUNKS
+  int du0, n_du;          // and routed down units of top_k * DN_TILES * DN_CHUNKS
+  int n_sd_real;          // shared down tiles without the padding tile that keeps the units on even slots
 };
 
 template <int D, int F>
-__device__ __forceinline__ TilePlan make_plan(const StackArgs& a) {
+__device__ __forceinline__ TilePlan make_plan(const StackArgs& a, bool tc) {
   using S = StackShape<D, F>;
   TilePlan p;
   const long long b = blockIdx.x, G = gridDim.x;
@@ -182,13 +210,24 @@ __device__ __forceinline__ TilePlan make_plan(const StackArgs& a) {
   const int qg = a.top_k * (2 * F / S::QG_ROWS);
   p.q0 = (int)(b * qg / G);
   p.n_q = (int)((b + 1) * qg / G) - p.q0;
+  const long long gu_units = (long long)a.top_k * S::GU_TILES * S::GU_CHUNKS;
+  p.qu0 = (int)(b * gu_units / G);
+  p.n_qu = (int)((b + 1) * gu_units / G) - p.qu0;
+  if (tc) p.n_q = 2 * p.n_qu;   // a unit takes two consecutive ring slots
   const int groups = D / S::RT;
   p.g0 = (int)(b * groups / G);
   p.n_g = (int)((b + 1) * groups / G) - p.g0;
   const int pad_r = (p.n_r + kSC - 1) / kSC * kSC;
   p.n_sg = (p.n_u + kSC - 1) / kSC * kSC * S::SG_SPLIT;
-  p.n_sd = a.n_shared * p.n_g * S::SD_PER_GROUP;
+  p.n_sd = p.n_sd_real = a.n_shared * p.n_g * S::SD_PER_GROUP;
   p.n_qd = a.top_k * p.n_g;
+  const long long dn_units = (long long)a.top_k * S::DN_TILES * S::DN_CHUNKS;
+  p.du0 = (int)(b * dn_units / G);
+  p.n_du = (int)((b + 1) * dn_units / G) - p.du0;
+  if (tc) {
+    p.n_sd += p.n_sd & 1;
+    p.n_qd = 2 * p.n_du;
+  }
   p.s_r = 0;
   p.s_sg = pad_r;
   p.s_qg = p.s_sg + p.n_sg;
@@ -212,6 +251,20 @@ struct StackShared {
   unsigned epoch1;                      // launches completed before this one, plus one: scales every target
   volatile int routed_layers;           // layers whose routing table is in `routes` (set by the auxiliary warp)
   volatile int failed;
+  // tensor-core path
+  uint64_t sf_full[kTcSfSlots], sf_empty[kTcSfSlots];   // weight scales of a unit are in tensor memory / may be overwritten
+  uint64_t d_full[2], d_empty[2];                        // accumulator of a tile segment is complete / has been read
+  uint32_t tmem_base;
+  volatile int x_ready;                 // layers whose activation digits and scales are staged
+  volatile int act_ready;               // layers whose routed activations are staged as digit rows
+  volatile int sg_done;                 // layers whose router rows and shared gate/up tiles this block has finished
+  volatile long long issued;            // ring tiles the producer has issued (published after every tensor-core unit)
+  int finisher;                         // this block stored the last part of the tile at hand
+  float act_inverse[kSMaxTopK];         // inverse normalisers of the routed activations' digit rows
+  uint8_t dn_parts[kSMaxTopK][32];      // blocks that share a down tile (route, row tile)
+  unsigned dn_target[32];               // arrivals that complete a row tile: routed parts of every route + shared-expert blocks
+  uint8_t sfbx[kTcDigits][256];         // E4M3 block scales of the digit rows of x
+  uint8_t sfba[4 * kSMaxTopK][128];     // and of the digit rows of the routed activations
 };
 
 __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
@@ -395,19 +448,154 @@ __device__ __forceinline__ void stage_x(uint16_t* s_x16, uint16_t* s_xbf, const 
   if (ct == 0) sh->x_inverse = inverse;
 }
 
+// Bounded wait on a barrier of the tensor-core path that also gives up as soon as the launch has failed.
+__device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity, StackShared* sh) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (sh->failed) return false;
+    if (clock64() - t0 > kWaitLimitCycles) {
+      sh->failed = 1;
+      return false;
+    }
+  }
+  return true;
+}
+// A parity wait on a ring slot is only meaningful once the slot's previous use is over. The consumer
+// warps get that from the order in which they take tiles; a warp that waits for a tile from far away
+// (the tensor-core warps may be a whole lap ahead of the consumers) first waits until the producer
+// has issued that very tile, which it does only after the slot's previous tile was consumed.
+__device__ __forceinline__ bool tc_wait_issued(long long tile, StackShared* sh) {
+  if (sh->issued > tile) {
+    __threadfence_block();
+    return true;
+  }
+  const long long t0 = clock64();
+  while (sh->issued <= tile) {
+    if (sh->failed) return false;
+    if (clock64() - t0 > kWaitLimitCycles) {
+      sh->failed = 1;
+      return false;
+    }
+  }
+  __threadfence_block();
+  return true;
+}
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
+__device__ __forceinline__ void tc_group_sync() { asm volatile("bar.sync 3, 256;" ::: "memory"); }
+
+// Items [first, last] of `total` dealt to `blocks` blocks as [total*b/blocks, total*(b+1)/blocks):
+// how many blocks hold some of them, and the position of block `me` among those.
+__device__ __forceinline__ int tc_split(long long first, long long last, long long total, int blocks, int me, int* my_index) {
+  const int fb = tc_owner(first, total, blocks), lb = tc_owner(last, total, blocks);
+  int parts = 0, index = 0;
+  for (int b = fb; b <= lb; ++b) {
+    if (total * b / blocks < total * (b + 1) / blocks) {   // blocks with an empty range hold nothing
+      if (b == me) index = parts;
+      ++parts;
+    }
+  }
+  *my_index = index;
+  return parts;
+}
+
+// Tensor-core variant: the same vector as BF16 (router, shared experts) and as four E2M1 digit rows
+// in the swizzled N-operand layout, block scales to `sh->sfbx`. All consumer threads. The digit rows
+// are made from the BF16 copy in a short rolled loop: this runs once per layer, and straight-line code
+// for sixteen elements per thread costs more in instruction fetch than in arithmetic.
+template <int D>
+__device__ __forceinline__ void stage_x_tc(unsigned char* s_xdig, uint16_t* s_xbf, const float (&value)[(D + kSC * 32 - 1) / (kSC * 32)],
+                                           float amax_bound, StackShared* sh, int ct) {
+  float inverse;
+  const uint32_t bits = f32_to_bf16_bits(amax_bound) & 0x7fffu;
+  const float scale = 512.f * pow2_normaliser(bits + 0x80u > 0x7f7fu ? 0x7f7fu : bits + 0x80u, &inverse);  // below 1024
+  constexpr int PER = D / (kSC * 32);
+  static_assert(D % (kSC * 32) == 0, "every thread stages whole blocks' worth of elements");
+#pragma unroll
+  for (int n = 0; n < PER; ++n) s_xbf[ct + n * (kSC * 32)] = (uint16_t)f32_to_bf16_bits(value[n]);
+  consumer_sync();
+#pragma unroll 1
+  for (int g = ct; g < D / 8; g += kSC * 32)
+    tc_stage8(reinterpret_cast<const uint4*>(s_xbf)[g], scale, s_xdig, 8, 0, g * 8, &sh->sfbx[0][0], 256);
+  if (ct == 0) sh->x_inverse = inverse * (1.f / 512.f);
+}
+
+// Block scales of `rows` digit rows (`bytes_per_row` each, row r at table + r * pitch) into the
+// activation-scale columns of tensor memory, 4 columns per 64-element step. Four warps, one per
+// tensor-memory subpartition, write the same words.
+__device__ __forceinline__ void tc_upload_scales(uint32_t tmem, int subpartition, const uint8_t* table, int pitch, int rows, int steps,
+                                                 int lane) {
+  const uint32_t base = tmem + ((uint32_t)(subpartition * 32) << 16) + kTcColSfb;
+  for (int s0 = 0; s0 < steps; s0 += 4) {
+    uint32_t r[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      r[j] = ((j & 3) == 0 && lane < rows) ? *reinterpret_cast<const uint32_t*>(table + (size_t)lane * pitch + (s0 + (j >> 2)) * 4) : 0u;
+    tc_st16(base + s0 * 4, r);
+  }
+  tc_wait_st();
+  tc_fence_before();
+}
+
+// Tensor-core variant: every part of row tile `tile` (the routed projections' parts and the shared
+// experts' rows) is in global memory. Sums them in a fixed order -- the parts of a route in block
+// order, the routes in choice order, then the shared experts -- and stores the rows into every
+// rank's inbox. Rows first, first + stride, ... of the tile.
 template <int D, int F>
-__global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
+__device__ __forceinline__ void finish_row_tile(const StackArgs& a, StackShared* sh, int layer, int par, int xpar, int tile, int first,
+                                                int stride) {
+  using S = StackShape<D, F>;
+  (void)layer;
+  for (int row = first; row < kTcRows; row += stride) {
+    const size_t at_row = (size_t)tile * kTcRows + row;
+    float total = 0.f;
+    for (int j = 0; j < a.top_k; ++j) {
+      const RouteEntry& r = sh->routes[par].route[j];
+      const int parts = sh->dn_parts[j][tile];
+      const float* part = a.dn_part + (size_t)(j * S::DN_TILES + tile) * S::DN_CHUNKS * kTcRows + row;
+      float acc = 0.f;
+      for (int p = 0; p < parts; ++p) acc += __ldcg(part + (size_t)p * kTcRows);
+      if (r.dn_codes) {
+        float inverse;
+        pow2_normaliser(__ldcg(a.act_amax + par * kSMaxTopK + j), &inverse);
+        const float down = round_bf16(acc * (r.dn_scale2 * (inverse * (1.f / 512.f))));
+        total += round_bf16(down * r.weight);
+      }
+    }
+    for (int e = 0; e < a.n_shared; ++e) total += __ldcg(a.sd_out + ((size_t)par * a.n_shared + e) * D + at_row);
+    const size_t at = ((size_t)xpar * a.world + a.rank) * D + at_row;
+    for (int r = 0; r < a.world; ++r) a.peer_inbox[r][at] = total;
+  }
+}
+// one thread, after every row of the tile has been stored: count the tile at every rank
+__device__ __forceinline__ void deliver_row_tile(const StackArgs& a, int layer) {
+  if (a.world > 1) {
+    __threadfence_system();
+    for (int r = 0; r < a.world; ++r) red_release_sys_add(a.peer_xsync[r] + layer, 1u);
+  } else {
+    __threadfence();
+    red_release_add(a.xsync + layer, 1u);
+  }
+}
+
+template <int D, int F, bool TC>
+__global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_kernel(StackArgs a) {
   using S = StackShape<D, F>;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ StackShared sh;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  unsigned char* slots = smem;
-  unsigned char* staging = smem + kSStages * kSSlot;
-  uint16_t* s_x16 = reinterpret_cast<uint16_t*>(staging);            // [D] FP16 normalised (gate/up phases)
-  uint16_t* s_xbf = s_x16 + D;                                        // [D] BF16
+  // TC: the layers carry TMA descriptors and the routed experts run on the tensor cores
+  constexpr bool tc = TC;
+  unsigned char* slots = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);   // swizzled tiles need 1024-byte alignment
+  unsigned char* staging = slots + kSStages * kSSlot;
+  uint16_t* s_x16 = reinterpret_cast<uint16_t*>(staging);            // [D] FP16 normalised (gate/up phases, CUDA-core path)
+  unsigned char* s_xdig = staging;                                    // [D/256][8 rows][128 B] digit rows of x (tensor-core path)
+  uint16_t* s_xbf = reinterpret_cast<uint16_t*>(staging + (tc ? D * 4 : D * 2));   // [D] BF16
   uint16_t* s_act = reinterpret_cast<uint16_t*>(staging);            // [top_k][F] FP16 normalised (down phases)
-  uint16_t* s_sact = s_act + (size_t)kSMaxTopK * F;                   // [n_shared][F] BF16 (act * gamma)
-  const TilePlan plan = make_plan<D, F>(a);
+  unsigned char* s_adig = staging;                                    // [F/256][32 rows][128 B] digit rows of the routed activations
+  uint16_t* s_sact = tc ? reinterpret_cast<uint16_t*>(staging + S::TC_SACT)
+                        : s_act + (size_t)kSMaxTopK * F;              // [n_shared][F] BF16 (act * gamma)
+  const TilePlan plan = make_plan<D, F>(a, tc);
   const int total_rows = a.experts + a.n_shared;
   const int n_jobs = a.top_k + a.n_shared;
 
@@ -416,6 +604,18 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
       mbar_init(&sh.full[s], 1);
       mbar_init(&sh.empty[s], 1);
     }
+    for (int s = 0; s < kTcSfSlots; ++s) {
+      mbar_init(&sh.sf_full[s], 4);
+      mbar_init(&sh.sf_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&sh.d_full[s], 1);
+      mbar_init(&sh.d_empty[s], 4);
+    }
+    sh.x_ready = 0;
+    sh.act_ready = 0;
+    sh.sg_done = 0;
+    sh.issued = 0;
     sh.routed_layers = 0;
     sh.failed = 0;
     sh.epoch1 = *a.epoch + 1u;
@@ -423,7 +623,33 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
     mbar_init_fence();
   }
   for (int i = threadIdx.x; i < (kSMaxTopK + kSMaxShared) * kSMaxRows; i += blockDim.x) (&sh.contrib[0][0])[i] = 0.f;
+  if (tc) {
+    if (warp == kSC + 1) tc_alloc(&sh.tmem_base, 512);
+    // how every down tile is split between blocks (the same for every layer)
+    const long long dn_units = (long long)a.top_k * S::DN_TILES * S::DN_CHUNKS;
+    for (int i = threadIdx.x; i < a.top_k * S::DN_TILES; i += blockDim.x) {
+      int unused;
+      sh.dn_parts[i / S::DN_TILES][i % S::DN_TILES] =
+          (uint8_t)tc_split((long long)i * S::DN_CHUNKS, (long long)i * S::DN_CHUNKS + S::DN_CHUNKS - 1, dn_units, gridDim.x, 0, &unused);
+    }
+    if (blockIdx.x == 0 && threadIdx.x < 2 * kSMaxTopK) a.act_amax[threadIdx.x] = 0u;   // seen by all before the first routing exists
+  }
+  tc_fence_before();
   __syncthreads();
+  tc_fence_after();
+  if (tc && threadIdx.x < S::DN_TILES) {
+    const int tile = threadIdx.x;
+    unsigned target = 0;
+    for (int j = 0; j < a.top_k; ++j) target += sh.dn_parts[j][tile];
+    if (a.n_shared > 0) {
+      int unused;
+      const int groups = D / S::RT;
+      target += (unsigned)tc_split(tile * kTcRows / S::RT, (tile * kTcRows + kTcRows - 1) / S::RT, groups, gridDim.x, 0, &unused);
+    }
+    sh.dn_target[tile] = target;
+  }
+  __syncthreads();
+  const uint32_t tmem = tc ? sh.tmem_base : 0u;
 
   if (warp == 0) {
     // =========================================================== producer (one lane)
@@ -445,6 +671,13 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
         ++issued;
         return true;
       };
+      // tensor-core variant: tell the waiters how far the issue has come (see tc_wait_issued)
+      auto publish = [&]() {
+        if (tc) {
+          __threadfence_block();
+          sh.issued = issued;
+        }
+      };
       unsigned char* dst = nullptr;
       uint64_t* bar = nullptr;
       constexpr int kQgPerJob = 2 * F / S::QG_ROWS;
@@ -460,6 +693,7 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
           } else {
             mbar_expect_tx(bar, 0);
           }
+          publish();
         }
         // ---- shared gate/up: blocks of kSC units, each unit SG_SPLIT column slabs
         for (int unit0 = 0; unit0 < plan.n_u && alive; unit0 += kSC) {
@@ -476,6 +710,7 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
               } else {
                 mbar_expect_tx(bar, 0);
               }
+              publish();
             }
           }
         }
@@ -486,7 +721,31 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
         INK_TRACE(layer, kTrProdRouteGot);
         const RouteTable& table = sh.routes[layer & 1];
         // ---- routed gate/up
-        {
+        if (tc) {
+          // units of 128 rows x 256 columns (codes and scales, two ring slots) for the tensor cores
+          const unsigned char* maps = reinterpret_cast<const unsigned char*>(ly.tmaps);
+          int chunk = plan.qu0 % S::GU_CHUNKS, tile = (plan.qu0 / S::GU_CHUNKS) % S::GU_TILES;
+          int choice = plan.qu0 / (S::GU_CHUNKS * S::GU_TILES);
+          for (int i = 0; i < plan.n_qu; ++i) {
+            unsigned char* second = nullptr;
+            uint64_t* bar2 = nullptr;
+            if (!(alive = next_slot(dst, bar)) || !(alive = next_slot(second, bar2))) break;
+            const RouteEntry& r = table.route[choice];
+            const int expert = r.gu_codes ? r.expert : 0;   // an inactive route streams expert 0 and is zeroed at the end
+            mbar_expect_tx(bar, kTcUnitBytes);
+            tc_tma_3d(dst, maps, chunk * 128, tile * kTcRows, expert, bar);
+            tc_tma_3d(dst + kTcCodeBytes, maps + 128, chunk * 16, tile * kTcRows, expert, bar);
+            mbar_expect_tx(bar2, 0);
+            publish();
+            if (++chunk == S::GU_CHUNKS) {
+              chunk = 0;
+              if (++tile == S::GU_TILES) {
+                tile = 0;
+                ++choice;
+              }
+            }
+          }
+        } else {
           int choice = plan.q0 / kQgPerJob, row0 = (plan.q0 % kQgPerJob) * S::QG_ROWS;
           for (int t = 0; t < plan.n_q; ++t) {
             if (!(alive = next_slot(dst, bar))) break;
@@ -512,10 +771,41 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
             if (!(alive = next_slot(dst, bar))) break;
             mbar_expect_tx(bar, S::SD_BYTES);
             bulk_g2s(dst, w + (size_t)t * S::SD_ROWS * F, S::SD_BYTES, bar);
+            publish();
+          }
+        }
+        if (tc && alive && (plan.n_sd_real & 1)) {   // keeps the units that follow on even slots
+          if (!(alive = next_slot(dst, bar))) break;
+          mbar_expect_tx(bar, 0);
+          publish();
+        }
+        // ---- routed down: units of 128 rows x 256 columns for the tensor cores
+        if (tc && alive) {
+          const unsigned char* maps = reinterpret_cast<const unsigned char*>(ly.tmaps);
+          int chunk = plan.du0 % S::DN_CHUNKS, tile = (plan.du0 / S::DN_CHUNKS) % S::DN_TILES;
+          int choice = plan.du0 / (S::DN_CHUNKS * S::DN_TILES);
+          for (int i = 0; i < plan.n_du; ++i) {
+            unsigned char* second = nullptr;
+            uint64_t* bar2 = nullptr;
+            if (!(alive = next_slot(dst, bar)) || !(alive = next_slot(second, bar2))) break;
+            const RouteEntry& r = table.route[choice];
+            const int expert = r.dn_codes ? r.expert : 0;
+            mbar_expect_tx(bar, kTcUnitBytes);
+            tc_tma_3d(dst, maps + 256, chunk * 128, tile * kTcRows, expert, bar);
+            tc_tma_3d(dst + kTcCodeBytes, maps + 384, chunk * 16, tile * kTcRows, expert, bar);
+            mbar_expect_tx(bar2, 0);
+            publish();
+            if (++chunk == S::DN_CHUNKS) {
+              chunk = 0;
+              if (++tile == S::DN_TILES) {
+                tile = 0;
+                ++choice;
+              }
+            }
           }
         }
         // ---- routed down: choice-major, then row group
-        for (int choice = 0; choice < a.top_k && alive; ++choice) {
+        for (int choice = 0; choice < a.top_k && alive && !tc; ++choice) {
           const RouteEntry& r = table.route[choice];
           for (int g = 0; g < plan.n_g; ++g) {
             if (!(alive = next_slot(dst, bar))) break;
@@ -533,12 +823,14 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
         for (int t = plan.s_pad; t < plan.per_layer && alive; ++t) {
           if (!(alive = next_slot(dst, bar))) break;
           mbar_expect_tx(bar, 0);
+          publish();
         }
         INK_TRACE(layer, kTrProdLayerIssued);
       }
     }
   } else if (warp == kSC + 1) {
     // =========================================================== auxiliary warp
+    long long tc_base = 0, qseq = 0, dseq = 0;   // ring index of the layer's first tile; units and tile segments so far
     for (int layer = 0; layer < a.n_layers; ++layer) {
       const unsigned* sync = a.sync + (size_t)layer * kSyncWordsPerLayer;
       // every block resolves the routing for itself (same inputs, same arithmetic, same result): the
@@ -548,9 +840,56 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       stack_router_tail(a, a.layers[layer], layer, &sh);
-      if (sh.failed) break;
+      if (tc && lane == 0 && !sh.failed) {
+        // ---- the routed projections on the tensor cores: one thread issues. A unit is 128 weight rows x
+        // 256 columns in two ring slots; four MMAs of 64 columns each accumulate it into the tile's accumulator.
+        auto issue = [&](volatile int* ready, int first_tile, int u0, int n_units, int chunks, const unsigned char* operand,
+                         int operand_chunk_bytes, uint32_t idesc) {
+          const long long t0 = clock64();
+          while (*ready <= layer && !sh.failed)
+            if (clock64() - t0 > kWaitLimitCycles) sh.failed = 1;
+          __threadfence_block();
+          tc_fence_after();
+          if (ready == &sh.act_ready) INK_TRACE(layer, kTrMmaDownStart);
+          int chunk = u0 % chunks;
+          for (int i = 0; i < n_units && !sh.failed; ++i) {
+            const long long t = tc_base + first_tile + 2 * i;
+            const int slot = (int)(t % kSStages), sfs = (int)(qseq % kTcSfSlots), dbuf = (int)(dseq & 1);
+            const bool seg_first = (i == 0 || chunk == 0), seg_last = (i + 1 == n_units || chunk == chunks - 1);
+            if (seg_first && !tc_wait(&sh.d_empty[dbuf], (uint32_t)((dseq >> 1) & 1) ^ 1u, &sh)) break;
+            if (!tc_wait_issued(t, &sh) || !tc_wait(&sh.full[slot], (uint32_t)(t / kSStages) & 1u, &sh)) break;
+            if (!tc_wait(&sh.sf_full[sfs], (uint32_t)(qseq / kTcSfSlots) & 1u, &sh)) break;
+            tc_fence_after();
+            const uint64_t ad = tc_desc_sw128(smem_u32(slots + (size_t)slot * kSSlot));
+            const uint64_t bd = tc_desc_sw128(smem_u32(operand + (size_t)chunk * operand_chunk_bytes));
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              tc_mma(tmem + kTcColD + dbuf * 32, ad + 2 * k, bd + 2 * k, idesc, (seg_first && k == 0) ? 0u : 1u,
+                     tmem + kTcColSfa + sfs * 16 + k * 4, tmem + kTcColSfb + (chunk * 4 + k) * 4);
+            tc_commit(&sh.empty[slot]);
+            tc_commit(&sh.empty[slot + 1]);
+            tc_commit(&sh.sf_empty[sfs]);
+            if (seg_last) {
+              tc_commit(&sh.d_full[dbuf]);
+              ++dseq;
+            }
+            ++qseq;
+            if (++chunk == chunks) chunk = 0;
+          }
+        };
+        INK_TRACE(layer, kTrMmaGuStart);
+        issue(&sh.x_ready, plan.s_qg, plan.qu0, plan.n_qu, S::GU_CHUNKS, s_xdig, 8 * 128, tc_idesc(8));
+        INK_TRACE(layer, kTrMmaGuEnd);
+        issue(&sh.act_ready, plan.s_qd, plan.du0, plan.n_du, S::DN_CHUNKS, s_adig, 32 * 128, tc_idesc(32));
+        INK_TRACE(layer, kTrMmaDownEnd);
+      }
+      tc_base += plan.per_layer;
+      // the warp leaves the loop together: lane 0 may have been issuing for a long time
+      __syncwarp();
+      const int failed = sh.failed;
+      if (__shfl_sync(0xffffffffu, failed, 0)) break;
     }
-  } else {
+  } else if (warp <= kSC) {
     // =========================================================== consumers
     const int cw = warp - 1, ct = threadIdx.x - 32;
     constexpr int PER = (D + kSC * 32 - 1) / (kSC * 32);
@@ -562,6 +901,7 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
       const long long i = base + t;
       slot = (int)(i % kSStages);
       bool ok = !sh.failed;
+      if (tc && ok) ok = tc_wait_issued(i, &sh);   // the slot's previous tile may have been a tensor-core unit
       if (ok) ok = mbar_wait(&sh.full[slot], (uint32_t)(i / kSStages) & 1);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
@@ -591,6 +931,26 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
       return done == n_tiles;
     };
 
+    const int sub = warp & 3;   // the tensor-memory subpartition this warp can reach
+    // stages the next activation vector for the gate/up phases; `ready` = layers staged once this returns
+    auto stage = [&](const float (&value)[PER], float amax_bound, int ready) {
+      if (!tc) {
+        stage_x<D>(s_x16, s_xbf, value, amax_bound, &sh, ct);
+        return;
+      }
+      stage_x_tc<D>(s_xdig, s_xbf, value, amax_bound, &sh, ct);
+      if (ct == 0 && ready >= 2) INK_TRACE(ready - 2, kTrXDigits);
+      tc_proxy_fence();   // the digit rows are read by the tensor core
+      consumer_sync();
+      if (ct == 0 && ready >= 2) INK_TRACE(ready - 2, kTrXVisible);
+      if (cw < 4) tc_upload_scales(tmem, sub, &sh.sfbx[0][0], 256, kTcDigits, D / 64, lane);
+      consumer_sync();
+      if (ct == 0) {
+        __threadfence_block();
+        sh.x_ready = ready;
+      }
+    };
+
     // ---- first activation vector
     {
       float value[PER];
@@ -607,7 +967,7 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
       consumer_sync();
       amax = 0.f;
       for (int w = 0; w < kSC; ++w) amax = fmaxf(amax, sh.red[w][0]);
-      stage_x<D>(s_x16, s_xbf, value, amax, &sh, ct);
+      stage(value, amax, 1);
       consumer_sync();
     }
 
@@ -620,15 +980,16 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
       // slot of the ranks' deliveries: alternates with every block of every launch
       const int xpar = (int)(((epoch1 - 1u) * (unsigned)a.n_layers + (unsigned)layer) & 1u);
       float* inbox = a.inbox + (size_t)xpar * a.world * D;
-      const unsigned down_target = epoch1 * gridDim.x * (unsigned)a.world;
+      // deliveries of a layer: one per block (CUDA-core variant) or per 128-row tile (tensor-core variant) and rank
+      const unsigned down_target = epoch1 * (tc ? (unsigned)S::DN_TILES : gridDim.x) * (unsigned)a.world;
       const float x_inverse = sh.x_inverse;
       const bool tracer = (ct == 0);
       if (tracer) INK_TRACE(layer, kTrLayerStart);
       // blocks that own no tile of a section still have to be counted
       if (ct == 0) {
         if (plan.n_sg == 0) red_release_add(sync + kShGuDone, 1u);
-        if (plan.n_q == 0) red_release_add(sync + kRtGuDone, 1u);
-        if (plan.n_sd + plan.n_qd == 0) {
+        if (plan.n_q == 0 && !tc) red_release_add(sync + kRtGuDone, 1u);   // (the tensor-core path counts tiles)
+        if (!tc && plan.n_sd + plan.n_qd == 0) {
           if (a.world > 1)
             for (int r = 0; r < a.world; ++r) red_release_sys_add(a.peer_xsync[r] + layer, 1u);
           else
@@ -711,8 +1072,17 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
         }
       }
       if (tracer) INK_TRACE(layer, kTrShGuDone);
+      if (tc) {
+        // this block is done with the BF16 copy of x: the tensor-core warps may overwrite it later on
+        consumer_sync();
+        if (ct == 0) {
+          __threadfence_block();
+          sh.sg_done = layer + 1;
+        }
+      }
       // ------------------------------------------------ routed gate/up
-      {
+      const unsigned rt_gu_target = epoch1 * gridDim.x;
+      if constexpr (!tc) {
         uint32_t xr[S::QG_CPL][16];
 #pragma unroll
         for (int j = 0; j < S::QG_CPL; ++j) {
@@ -781,6 +1151,10 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
         int slot;
         if (!take(t, src, slot)) break;
         const int i = t - plan.s_sd;
+        if (i >= plan.n_sd_real) {   // the padding tile of the tensor-core variant
+          release(slot);
+          continue;
+        }
         const int per_e = plan.n_g * S::SD_PER_GROUP;
         const int e = i / per_e, rem = i % per_e;
         const int local0 = (rem / S::SD_PER_GROUP) * S::RT + (rem % S::SD_PER_GROUP) * S::SD_ROWS;
@@ -794,15 +1168,39 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
             acc = dot8(*reinterpret_cast<const uint4*>(src + (size_t)row * F * 2 + chunk * 16), xs[chunk], acc);
           }
           acc = warp_sum(acc);
-          if (lane == 0) sh.contrib[a.top_k + e][local0 + row] = round_bf16(acc);
+          if (lane == 0) {
+            if (tc) a.sd_out[((size_t)par * a.n_shared + e) * D + (size_t)plan.g0 * S::RT + local0 + row] = round_bf16(acc);
+            else sh.contrib[a.top_k + e][local0 + row] = round_bf16(acc);
+          }
         }
         release(slot);
-        // down tiles are counted together (shared + routed)
-        section_done(layer, 2, plan.n_sd + plan.n_qd, false);
+        if (!tc) {
+          // down tiles are counted together (shared + routed)
+          section_done(layer, 2, plan.n_sd + plan.n_qd, false);
+        } else if (section_done(layer, 2, plan.n_sd_real, t + kSC >= plan.s_sd + plan.n_sd_real) && !sh.failed) {
+          // the block's shared-expert rows are in global memory: count the block at every 128-row tile it
+          // touches; whoever completes a tile (this warp or a tensor-core epilogue) sums and delivers it
+          const int row_a = plan.g0 * S::RT, row_b = (plan.g0 + plan.n_g) * S::RT - 1;
+          for (int tile = row_a / kTcRows; tile <= row_b / kTcRows; ++tile) {
+            int last = 0;
+            if (lane == 0)
+              last = atomicAdd(a.tilesync + (size_t)layer * kTileCountersPerLayer + kSMaxTopK * 32 + tile, 1u) + 1u ==
+                     epoch1 * sh.dn_target[tile];
+            if (__shfl_sync(0xffffffffu, last, 0)) {
+              __threadfence();
+              finish_row_tile<D, F>(a, &sh, layer, par, xpar, tile, lane, 32);
+              if (a.world > 1) __threadfence_system();
+              else __threadfence();
+              __syncwarp();
+              if (lane == 0) deliver_row_tile(a, layer);
+            }
+          }
+        }
       }
       if (tracer) INK_TRACE(layer, kTrShDownDone);
+      if constexpr (!tc) {
       // ------------------------------------------------ routed down
-      if (lane == 0) wait_global(sync + kRtGuDone, epoch1 * gridDim.x, &sh);
+      if (lane == 0) wait_global(sync + kRtGuDone, rt_gu_target, &sh);
       __syncwarp();
       if (tracer) INK_TRACE(layer, kTrRtGuAll);
       if (!sh.failed) {
@@ -862,13 +1260,6 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
           }
           if (section_done(layer, 2, plan.n_sd + plan.n_qd, false)) last_of_block = true;
         }
-        // padding tiles at the end of the layer
-        for (int t = first_of(plan.s_pad); t < plan.per_layer; t += kSC) {
-          const unsigned char* src;
-          int slot;
-          if (!take(t, src, slot)) break;
-          release(slot);
-        }
         // The warp that finished the block's last down tile sums the contributions in a
         // fixed order (routes in choice order, then the shared experts) and publishes them.
         // (Routed-down tiles start only after every shared-down tile of the block is done, so
@@ -894,6 +1285,14 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
           }
         }
       }
+      }   // CUDA-core routed down
+      // padding tiles at the end of the layer
+      for (int t = first_of(plan.s_pad); t < plan.per_layer; t += kSC) {
+        const unsigned char* src;
+        int slot;
+        if (!take(t, src, slot)) break;
+        release(slot);
+      }
       if (tracer) INK_TRACE(layer, kTrRtDownDone);
       // every block of every rank has delivered this layer's rows
       if (lane == 0) {
@@ -913,6 +1312,9 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
           }
         break;
       }
+      // the other set of activation maxima is free (its readers finished before this layer's deliveries
+      // completed) and is needed clean by the next layer
+      if (tc && blockIdx.x == 0 && ct < kSMaxTopK) a.act_amax[((layer + 1) & 1) * kSMaxTopK + ct] = 0u;
       // ------------------------------------------------ residual add + RMS norm (every block, redundantly)
       float value[PER];
       {
@@ -929,16 +1331,20 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
           const int i = ct + n * (kSC * 32);
           const bool ok = live && i < D;
           res[n] = ok ? __ldcg(res_in + i) : (uint16_t)0;
-          // every rank's delivery, summed in rank order (same bits on every rank); predicated loads of a
-          // fixed trip count so that they all issue before the first add
-          float got[kSMaxWorld];
-#pragma unroll
-          for (int r = 0; r < kSMaxWorld; ++r) got[r] = (ok && r < world) ? __ldcg(inbox + (size_t)r * D + i) : 0.f;
-          float sum = 0.f;
-#pragma unroll
-          for (int r = 0; r < kSMaxWorld; ++r) sum += got[r];
-          part[n] = sum;
           nw[n] = ok ? norm_weight[i] : (uint16_t)0;
+          part[n] = 0.f;
+        }
+        // every rank's delivery, summed in rank order (same bits on every rank); one rank at a time so that
+        // a rank's loads are all in flight together without holding world x PER registers
+        for (int r = 0; r < world; ++r) {
+          float got[PER];
+#pragma unroll
+          for (int n = 0; n < PER; ++n) {
+            const int i = ct + n * (kSC * 32);
+            got[n] = (live && i < D) ? __ldcg(inbox + (size_t)r * D + i) : 0.f;
+          }
+#pragma unroll
+          for (int n = 0; n < PER; ++n) part[n] += got[n];
         }
 #pragma unroll
         for (int n = 0; n < PER; ++n) {
@@ -988,7 +1394,7 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
             }
           }
         } else {
-          stage_x<D>(s_x16, s_xbf, value, amax_h * scale * amax_w, &sh, ct);
+          stage(value, amax_h * scale * amax_w, layer + 2);
           // contributions of inactive routes must read as zero in the next layer too
           for (int i = ct; i < (kSMaxTopK + kSMaxShared) * kSMaxRows; i += kSC * 32) (&sh.contrib[0][0])[i] = 0.f;
           if (ct < 3) sh.done[par ^ 1][ct] = 0;
@@ -997,8 +1403,206 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
         if (tracer) INK_TRACE(layer, kTrNormDone);
       }
     }
+  } else if constexpr (TC) {
+    // =========================================================== tensor-core warps
+    // Warps 0..3 of the group move the weight scales of every unit from shared to tensor memory,
+    // warps 4..7 read the accumulators; all eight turn the routed activations into digit rows.
+    const int tw = warp - (kSC + 2), tt = threadIdx.x - (kSC + 2) * 32, et = tt - 128;
+    const int sub = warp & 3;                                   // the tensor-memory subpartition this warp can reach
+    const uint32_t lane_base = (uint32_t)(sub * 32) << 16;
+    const int row = sub * 32 + lane;                            // accumulator row of this thread
+    long long base = 0, qseq = 0, dseq = 0;                     // ring index of the layer's first tile; units, tile segments so far
+    // weight scales of `n_units` units whose first ring slots are first_tile, first_tile + 2, ...
+    auto scales_loop = [&](int first_tile, int n_units) {
+      for (int i = 0; i < n_units; ++i) {
+        const long long t = base + first_tile + 2 * i;
+        const int slot = (int)(t % kSStages), sfs = (int)(qseq % kTcSfSlots);
+        bool ok = tc_wait_issued(t, &sh) && tc_wait(&sh.full[slot], (uint32_t)(t / kSStages) & 1u, &sh);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        // lane = row % 32, column = row / 32, four scale bytes (one 64-column MMA step) per column
+        const unsigned char* sc = slots + (size_t)slot * kSSlot + kTcCodeBytes;
+        const uint4 r0 = *reinterpret_cast<const uint4*>(sc + lane * 16);
+        const uint4 r1 = *reinterpret_cast<const uint4*>(sc + (lane + 32) * 16);
+        const uint4 r2 = *reinterpret_cast<const uint4*>(sc + (lane + 64) * 16);
+        const uint4 r3 = *reinterpret_cast<const uint4*>(sc + (lane + 96) * 16);
+        ok = tc_wait(&sh.sf_empty[sfs], (uint32_t)((qseq / kTcSfSlots) & 1) ^ 1u, &sh);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t w[16] = {r0.x, r1.x, r2.x, r3.x, r0.y, r1.y, r2.y, r3.y, r0.z, r1.z, r2.z, r3.z, r0.w, r1.w, r2.w, r3.w};
+        tc_st16(tmem + lane_base + kTcColSfa + sfs * 16, w);
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh.sf_full[sfs]);
+        ++qseq;
+      }
+    };
+    // sum of the four digit columns starting at `column` of the next tile segment's accumulator
+    // (after a failed wait the four warps still walk the same barriers: nobody is left behind at one)
+    auto read_segment = [&](int column) -> float {
+      const int dbuf = (int)(dseq & 1);
+      bool ok = tc_wait(&sh.d_full[dbuf], (uint32_t)((dseq >> 1) & 1), &sh);
+      ok = __all_sync(0xffffffffu, ok);
+      float sum = 0.f;
+      if (ok) {
+        tc_fence_after();
+        float v[4];
+        tc_ld4(tmem + lane_base + kTcColD + dbuf * 32 + column, v);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh.d_empty[dbuf]);
+        sum = (v[0] + v[1]) + (v[2] + v[3]);
+      }
+      ++dseq;
+      return sum;
+    };
+
+    for (int layer = 0; layer < a.n_layers; ++layer, base += plan.per_layer) {
+      unsigned* sync = a.sync + (size_t)layer * kSyncWordsPerLayer;
+      unsigned* tile_count = a.tilesync + (size_t)layer * kTileCountersPerLayer;
+      const int par = layer & 1;
+      const unsigned epoch1 = sh.epoch1;
+      const int xpar = (int)(((epoch1 - 1u) * (unsigned)a.n_layers + (unsigned)layer) & 1u);
+      const bool tracer = (et == 0);
+      // ------------------------------------------------ routed gate/up
+      if (tw < 4) {
+        scales_loop(plan.s_qg, plan.n_qu);
+        if (tt == 0) INK_TRACE(layer, kTrScalesGuEnd);
+      } else {
+        // SwiGLU where the tile is complete in this block; otherwise the part goes to global memory
+        // and the block that stores the last part of the tile finishes it
+        const long long total = (long long)a.top_k * S::GU_TILES * S::GU_CHUNKS;
+        int u = plan.qu0;
+        const int end = plan.qu0 + plan.n_qu;
+        while (u < end) {
+          const int tg = u / S::GU_CHUNKS;
+          float sum = read_segment(0);
+          int index;
+          const int parts = tc_split((long long)tg * S::GU_CHUNKS, (long long)tg * S::GU_CHUNKS + S::GU_CHUNKS - 1, total,
+                                     gridDim.x, blockIdx.x, &index);
+          bool finish = true;
+          if (parts > 1) {
+            float* part = a.gu_part + (size_t)tg * S::GU_CHUNKS * kTcRows;
+            part[(size_t)index * kTcRows + row] = sum;
+            __threadfence();   // every writer pushes its own store out before the count moves
+            epilogue_sync();
+            if (et == 0) {
+              __threadfence();
+              sh.finisher = atomicAdd(tile_count + tg, 1u) + 1u == epoch1 * (unsigned)parts;
+            }
+            epilogue_sync();
+            finish = sh.finisher != 0;
+            if (finish) {
+              __threadfence();
+              sum = 0.f;
+              for (int p = 0; p < parts; ++p) sum += __ldcg(part + (size_t)p * kTcRows + row);   // fixed order
+            }
+          }
+          if (finish) {
+            const int choice = tg / S::GU_TILES, tile = tg % S::GU_TILES;
+            const RouteEntry r = sh.routes[par].route[choice];
+            const float mine = sum * (r.gu_scale2 * sh.x_inverse);
+            const float up = __shfl_xor_sync(0xffffffffu, mine, 1);   // even rows are gate, odd rows up
+            uint32_t bits = 0;
+            if ((lane & 1) == 0) {
+              bits = r.gu_codes ? f32_to_bf16_bits(silu_mul(mine, up)) : 0u;
+              a.activated[((size_t)par * a.top_k + choice) * F + tile * (kTcRows / 2) + (row >> 1)] = (uint16_t)bits;
+            }
+            // largest magnitude of the route's activations, for the normaliser of their digit rows
+            bits &= 0x7fffu;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) bits = max(bits, __shfl_xor_sync(0xffffffffu, bits, o));
+            if (lane == 0) atomicMax(a.act_amax + par * kSMaxTopK + choice, bits);
+            __threadfence();
+            epilogue_sync();
+            if (et == 0) {
+              __threadfence();
+              red_release_add(sync + kRtGuDone, 1u);
+            }
+          }
+          u = min(end, (tg + 1) * S::GU_CHUNKS);
+        }
+      }
+      if (tracer) INK_TRACE(layer, kTrRtGuDone);
+      // ------------------------------------------------ routed activations -> digit rows (all eight warps)
+      if (lane == 0) {
+        wait_global(sync + kRtGuDone, epoch1 * (unsigned)(a.top_k * S::GU_TILES), &sh);
+        wait_routing(layer, &sh);
+        const long long t0 = clock64();
+        while (sh.sg_done <= layer && !sh.failed)
+          if (clock64() - t0 > kWaitLimitCycles) sh.failed = 1;
+        __threadfence_block();
+      }
+      __syncwarp();
+      if (tracer) INK_TRACE(layer, kTrRtGuAll);
+      {
+        // groups of 8 consecutive activations, consecutive groups to consecutive threads; a rolled loop
+        // with the next group's load in flight
+        constexpr int kGroups = F / 8;   // per route
+        const int total = a.top_k * kGroups;
+        const bool live = !sh.failed;
+        const uint4* src = reinterpret_cast<const uint4*>(a.activated + (size_t)par * a.top_k * F);
+        uint4 ahead = (live && tt < total) ? __ldcg(src + tt) : make_uint4(0, 0, 0, 0);
+#pragma unroll 1
+        for (int g = tt; g < total; g += 256) {
+          const uint4 raw = ahead;
+          if (g + 256 < total) ahead = live ? __ldcg(src + g + 256) : make_uint4(0, 0, 0, 0);
+          const int j = g / kGroups;
+          float inverse;
+          const float scale = 512.f * pow2_normaliser(__ldcg(a.act_amax + par * kSMaxTopK + j), &inverse);   // below 1024
+          tc_stage8(raw, scale, s_adig, 32, 4 * j, (g % kGroups) * 8, &sh.sfba[0][0], 128);
+        }
+      }
+      tc_proxy_fence();   // the digit rows are read by the tensor core
+      tc_group_sync();
+      if (tw < 4) tc_upload_scales(tmem, sub, &sh.sfba[0][0], 128, 4 * a.top_k, F / 64, lane);
+      tc_group_sync();
+      if (tt == 0) {
+        __threadfence_block();
+        sh.act_ready = layer + 1;
+      }
+      if (tracer) INK_TRACE(layer, kTrActStaged);
+      // ------------------------------------------------ routed down
+      if (tw < 4) {
+        scales_loop(plan.s_qd, plan.n_du);
+        if (tt == 0) INK_TRACE(layer, kTrScalesDownEnd);
+      } else {
+        const long long total = (long long)a.top_k * S::DN_TILES * S::DN_CHUNKS;
+        int u = plan.du0;
+        const int end = plan.du0 + plan.n_du;
+        while (u < end) {
+          const int tg = u / S::DN_CHUNKS;
+          const int j = tg / S::DN_TILES, tile = tg % S::DN_TILES;
+          const float sum = read_segment(4 * j);
+          int index;
+          tc_split((long long)tg * S::DN_CHUNKS, (long long)tg * S::DN_CHUNKS + S::DN_CHUNKS - 1, total, gridDim.x, blockIdx.x, &index);
+          a.dn_part[((size_t)tg * S::DN_CHUNKS + index) * kTcRows + row] = sum;
+          __threadfence();
+          epilogue_sync();
+          if (et == 0) {
+            __threadfence();
+            sh.finisher = atomicAdd(tile_count + kSMaxTopK * 32 + tile, 1u) + 1u == epoch1 * sh.dn_target[tile];
+          }
+          epilogue_sync();
+          if (sh.finisher) {   // every part of the row tile is in: sum and deliver it
+            __threadfence();
+            finish_row_tile<D, F>(a, &sh, layer, par, xpar, tile, et, 128);
+            if (a.world > 1) __threadfence_system();
+            else __threadfence();
+            epilogue_sync();
+            if (et == 0) deliver_row_tile(a, layer);
+          }
+          u = min(end, (tg + 1) * S::DN_CHUNKS);
+        }
+      }
+      if (tracer) INK_TRACE(layer, kTrRtDownDone);
+    }
   }
+  tc_fence_before();
   __syncthreads();
+  if (tc && warp == kSC + 1) tc_dealloc(tmem, 512);
   if (threadIdx.x == 0 && sh.failed && a.status) atomicOr(a.status, kFlagWaitTimedOut);
   // Every block read the epoch before it could pass any counter, and block 0 gets here only after
   // the last counter of the launch, so this store cannot be seen by a block of the same launch.
@@ -1006,22 +1610,23 @@ __global__ void __launch_bounds__(kSThreads, 1) moe_stack_kernel(StackArgs a) {
 }
 
 // ------------------------------------------------------------------- host side
-template <int D, int F>
+template <int D, int F, bool TC>
 static int launch_stack(const StackArgs& a, cudaStream_t stream) {
   using S = StackShape<D, F>;
+  constexpr int threads = TC ? kSThreadsTc : kSThreads;
   static bool configured = false;
   static int sms = 0;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(moe_stack_kernel<D, F>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM);
+    cudaError_t e = cudaFuncSetAttribute(moe_stack_kernel<D, F, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM);
     INK_REQUIRE(e == cudaSuccess, kLaunchFailed, "moe_stack: %d bytes of shared memory refused: %s", S::SMEM,
                 cudaGetErrorString(e));
-    INK_PREFER_MAX_SMEM((moe_stack_kernel<D, F>));
+    INK_PREFER_MAX_SMEM((moe_stack_kernel<D, F, TC>));
     int device = 0, coop = 0, per_sm = 0;
     cudaGetDevice(&device);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
     cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device);
     INK_REQUIRE(coop, kLaunchFailed, "moe_stack: the device cannot launch cooperative kernels");
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, moe_stack_kernel<D, F>, kSThreads, S::SMEM);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, moe_stack_kernel<D, F, TC>, threads, S::SMEM);
     INK_REQUIRE(e == cudaSuccess && per_sm >= 1, kLaunchFailed, "moe_stack: the kernel does not fit on an SM");
     configured = true;
   }
@@ -1030,8 +1635,8 @@ static int launch_stack(const StackArgs& a, cudaStream_t stream) {
   INK_REQUIRE(rows_per_block <= kSMaxRows, kUnsupportedShape, "moe_stack: %d output rows per block", rows_per_block);
   StackArgs args = a;
   void* params[] = {&args};
-  cudaError_t e = cudaLaunchCooperativeKernel((const void*)moe_stack_kernel<D, F>, dim3(sms), dim3(kSThreads), params,
-                                  (size_t)S::SMEM, stream);
+  cudaError_t e = cudaLaunchCooperativeKernel((const void*)moe_stack_kernel<D, F, TC>, dim3(sms), dim3(threads), params,
+                                              (size_t)S::SMEM, stream);
   INK_REQUIRE(e == cudaSuccess, kLaunchFailed, "moe_stack: launch failed: %s", cudaGetErrorString(e));
   return kOk;
 }
@@ -1042,7 +1647,68 @@ using namespace ink;
 
 extern "C" size_t ink_moe_stack_layer_bytes(void) { return sizeof(StackLayer); }
 
+// ---- TMA descriptors of a layer's banks (driver entry point resolved at first use; no link to libcuda)
+typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                      const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                      CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static TensorMapEncodeFn tensor_map_encoder() {
+  static TensorMapEncodeFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (TensorMapEncodeFn)p;
+  }
+  return fn;
+}
+// bytes [row_bytes] x rows x experts, box of `box_bytes` x 128 rows x 1 expert
+static int encode_bank(CUtensorMap* out, const void* base, uint64_t expert_stride, int experts, int rows, int row_bytes,
+                       int box_bytes, bool swizzle) {
+  TensorMapEncodeFn enc = tensor_map_encoder();
+  INK_REQUIRE(enc != nullptr, kLaunchFailed, "encode_banks: the driver has no cuTensorMapEncodeTiled");
+  INK_REQUIRE(base != nullptr && aligned16(base) && expert_stride % 16 == 0 && expert_stride >= (uint64_t)rows * row_bytes,
+              kBadArgument, "encode_banks: bank at %p with expert stride %llu", base, (unsigned long long)expert_stride);
+  cuuint64_t dims[3] = {(cuuint64_t)row_bytes, (cuuint64_t)rows, (cuuint64_t)experts};
+  cuuint64_t strides[2] = {(cuuint64_t)row_bytes, (cuuint64_t)expert_stride};
+  cuuint32_t box[3] = {(cuuint32_t)box_bytes, (cuuint32_t)kTcRows, 1}, elem[3] = {1, 1, 1};
+  const CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, elem,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  INK_REQUIRE(r == CUDA_SUCCESS, kBadArgument, "encode_banks: cuTensorMapEncodeTiled returned %d", (int)r);
+  return kOk;
+}
+
+extern "C" int ink_moe_stack_encode_banks(void* out_host_512, const void* gate_up_codes, uint64_t gate_up_codes_stride,
+                                          const void* gate_up_scales, uint64_t gate_up_scales_stride, const void* down_codes,
+                                          uint64_t down_codes_stride, const void* down_scales, uint64_t down_scales_stride,
+                                          int experts, int hidden, int intermediate) {
+  INK_REQUIRE(out_host_512 != nullptr && experts >= 1, kBadArgument, "encode_banks: null output or no experts");
+  INK_REQUIRE(hidden % kTcChunkK == 0 && intermediate % kTcChunkK == 0 && (2 * intermediate) % kTcRows == 0 &&
+                  hidden % kTcRows == 0,
+              kUnsupportedShape, "encode_banks: hidden=%d intermediate=%d do not tile by 128 rows x 256 columns", hidden,
+              intermediate);
+  CUtensorMap maps[4];
+  int rc = encode_bank(&maps[0], gate_up_codes, gate_up_codes_stride, experts, 2 * intermediate, hidden / 2, 128, true);
+  if (rc == kOk) rc = encode_bank(&maps[1], gate_up_scales, gate_up_scales_stride, experts, 2 * intermediate, hidden / 16, 16, false);
+  if (rc == kOk) rc = encode_bank(&maps[2], down_codes, down_codes_stride, experts, hidden, intermediate / 2, 128, true);
+  if (rc == kOk) rc = encode_bank(&maps[3], down_scales, down_scales_stride, experts, hidden, intermediate / 16, 16, false);
+  if (rc != kOk) return rc;
+  static_assert(sizeof(CUtensorMap) == 128, "a TMA descriptor is 128 bytes");
+  memcpy(out_host_512, maps, sizeof(maps));
+  return kOk;
+}
+
 static size_t pad256(size_t n) { return (n + 255) / 256 * 256; }
+constexpr int kTileCounters = kTileCountersPerLayer;
+static size_t dn_part_bytes(int hidden, int intermediate, int top_k) {
+  return sizeof(float) * kTcRows * (size_t)top_k * (size_t)((hidden + kTcRows - 1) / kTcRows) *
+         (size_t)((intermediate + kTcChunkK - 1) / kTcChunkK);
+}
+static size_t gu_part_bytes(int hidden, int intermediate, int top_k) {
+  return sizeof(float) * kTcRows * (size_t)top_k * (size_t)((2 * intermediate + kTcRows - 1) / kTcRows) *
+         (size_t)((hidden + kTcChunkK - 1) / kTcChunkK);
+}
 
 // The region other ranks write into: delivered-block counters, then the delivered rows.
 extern "C" size_t ink_moe_stack_symmetric_bytes(int n_layers, int hidden, int world) {
@@ -1055,6 +1721,11 @@ extern "C" size_t ink_moe_stack_scratch_bytes(int n_layers, int hidden, int inte
   bytes += pad256(sizeof(unsigned) * kSyncWordsPerLayer * (size_t)n_layers);   // sync
   bytes += pad256(sizeof(unsigned));                                            // epoch
   bytes += pad256(sizeof(RouteTable) * (size_t)n_layers);                       // routes
+  bytes += pad256(gu_part_bytes(hidden, intermediate, top_k));                  // parts of split gate/up tiles
+  bytes += pad256(dn_part_bytes(hidden, intermediate, top_k));                  // parts of split down tiles
+  bytes += pad256(sizeof(float) * 2 * (size_t)n_shared * hidden);               // shared experts' down rows
+  bytes += pad256(sizeof(unsigned) * 2 * kSMaxTopK);                            // activation maxima
+  bytes += pad256(sizeof(unsigned) * kTileCounters * (size_t)n_layers);         // tile counters
   bytes += pad256(sizeof(float) * 2 * (size_t)(experts + n_shared));            // logits
   bytes += pad256(sizeof(float) * 2 * (size_t)experts);                         // scores
   bytes += pad256(2 * 2 * (size_t)top_k * intermediate);                        // activated
@@ -1072,11 +1743,14 @@ extern "C" size_t ink_moe_stack_trace_offset(int n_layers, int hidden, int inter
 }
 
 static int stack_decode(const void* layers, int n_layers, const void* x, void* residual_io, void* normed_out,
-                        float* partial_out, int glue, float eps, int hidden, int intermediate, int experts,
+                        float* partial_out, int flags, float eps, int hidden, int intermediate, int experts,
                         int n_shared, int top_k, void* scratch, size_t scratch_bytes, int rank, int world,
                         const uint64_t* peer_regions, int32_t* status, ink_stream_t stream) {
   INK_REQUIRE(layers && x && partial_out && scratch, kBadArgument, "moe_stack: null pointer argument");
-  INK_REQUIRE(n_layers >= 1 && (glue == 0 || glue == 1), kBadArgument, "moe_stack: n_layers=%d glue=%d", n_layers, glue);
+  INK_REQUIRE(flags >= 0 && flags <= 3, kBadArgument, "moe_stack: flags=%d", flags);
+  const int glue = flags & 1;
+  const bool banks_mapped = (flags & 2) != 0;   // every layer carries the TMA descriptors of its banks
+  INK_REQUIRE(n_layers >= 1, kBadArgument, "moe_stack: n_layers=%d", n_layers);
   INK_REQUIRE(glue || n_layers == 1, kBadArgument, "moe_stack: without the glue only one block can run");
   INK_REQUIRE(!glue || (residual_io && normed_out), kBadArgument, "moe_stack: glue mode needs residual and normed buffers");
   INK_REQUIRE(top_k >= 1 && top_k <= kSMaxTopK && n_shared >= 0 && n_shared <= kSMaxShared && experts >= top_k &&
@@ -1106,6 +1780,11 @@ static int stack_decode(const void* layers, int n_layers, const void* x, void* r
   a.sync = (unsigned*)take(sizeof(unsigned) * kSyncWordsPerLayer * (size_t)n_layers);
   a.epoch = (unsigned*)take(sizeof(unsigned));
   a.routes = (RouteTable*)take(sizeof(RouteTable) * (size_t)n_layers);
+  a.gu_part = (float*)take(gu_part_bytes(hidden, intermediate, top_k));
+  a.dn_part = (float*)take(dn_part_bytes(hidden, intermediate, top_k));
+  a.sd_out = (float*)take(sizeof(float) * 2 * (size_t)n_shared * hidden);
+  a.act_amax = (unsigned*)take(sizeof(unsigned) * 2 * kSMaxTopK);
+  a.tilesync = (unsigned*)take(sizeof(unsigned) * kTileCounters * (size_t)n_layers);
   a.logits = (float*)take(sizeof(float) * 2 * (size_t)(experts + n_shared));
   a.scores = (float*)take(sizeof(float) * 2 * (size_t)experts);
   a.activated = (uint16_t*)take(2 * 2 * (size_t)top_k * intermediate);
@@ -1140,7 +1819,7 @@ static int stack_decode(const void* layers, int n_layers, const void* x, void* r
 #define INK_STACK_CASE(DD, FF)                   \
   if (hidden == DD && intermediate == FF) {      \
     built = true;                                \
-    rc = launch_stack<DD, FF>(a, s);             \
+    rc = banks_mapped ? launch_stack<DD, FF, true>(a, s) : launch_stack<DD, FF, false>(a, s); \
   }
   INK_STACK_CASE(4096, 2048)
   INK_STACK_CASE(4096, 1024)
@@ -1160,18 +1839,18 @@ static int stack_decode(const void* layers, int n_layers, const void* x, void* r
 }
 
 extern "C" int ink_moe_stack_decode(const void* layers, int n_layers, const void* x, void* residual_io,
-                                    void* normed_out, float* partial_out, int glue, float eps, int hidden,
+                                    void* normed_out, float* partial_out, int flags, float eps, int hidden,
                                     int intermediate, int experts, int n_shared, int top_k, void* scratch,
                                     size_t scratch_bytes, int32_t* status, ink_stream_t stream) {
-  return stack_decode(layers, n_layers, x, residual_io, normed_out, partial_out, glue, eps, hidden, intermediate,
+  return stack_decode(layers, n_layers, x, residual_io, normed_out, partial_out, flags, eps, hidden, intermediate,
                       experts, n_shared, top_k, scratch, scratch_bytes, 0, 1, nullptr, status, stream);
 }
 
 extern "C" int ink_moe_stack_decode_tp(const void* layers, int n_layers, const void* x, void* residual_io,
-                                       void* normed_out, float* partial_out, int glue, float eps, int hidden,
+                                       void* normed_out, float* partial_out, int flags, float eps, int hidden,
                                        int intermediate, int experts, int n_shared, int top_k, void* scratch,
                                        size_t scratch_bytes, int rank, int world, const uint64_t* peer_regions,
                                        int32_t* status, ink_stream_t stream) {
-  return stack_decode(layers, n_layers, x, residual_io, normed_out, partial_out, glue, eps, hidden, intermediate,
+  return stack_decode(layers, n_layers, x, residual_io, normed_out, partial_out, flags, eps, hidden, intermediate,
                       experts, n_shared, top_k, scratch, scratch_bytes, rank, world, peer_regions, status, stream);
 }

@@ -1,6 +1,8 @@
 """One-launch decode of a stack of MoE blocks (ink_moe_stack_decode)."""
 from __future__ import annotations
 
+import ctypes
+import os
 import struct
 
 import torch
@@ -8,7 +10,14 @@ import torch
 from . import _abi
 
 BUILT_SHAPES = {(4096, 2048), (4096, 1024), (4096, 512), (4096, 256), (2048, 256), (1024, 512)}
-_LAYER_FORMAT = "<11Qfi"   # eleven pointers, route_scale, pad
+_LAYER_FORMAT = "<12Qfi"   # twelve pointers (the last: the banks' TMA descriptors or 0), route_scale, pad
+
+
+def tensor_cores_requested() -> bool:
+    """INKLING_STACK_TENSOR_CORES=1 runs the routed experts of the one-launch kernel on the tensor cores
+    (tcgen05 block-scaled MMA on the packed NVFP4 banks). Off by default: the variant is parity-green but
+    its per-layer staging and tile hand-over still cost more than its faster weight stream saves."""
+    return os.environ.get("INKLING_STACK_TENSOR_CORES", "0") == "1"
 
 
 def stack_supported(hidden: int, intermediate: int, experts: int, n_shared: int, top_k: int) -> bool:
@@ -26,11 +35,27 @@ class StackDescriptor:
         self.n_layers, self.hidden, self.intermediate = len(blocks), hidden, intermediate
         self.experts, self.n_shared, self.top_k = experts, n_shared, top_k
         ptr = lambda t: 0 if t is None else t.data_ptr()  # noqa: E731
+        # TMA descriptors of the banks, when every block's banks are evenly spaced in memory: the routed
+        # experts then run on the tensor cores
+        layouts = [b.get("bank_layout") for b in blocks]
+        self.bank_maps = None
+        maps_at = [0] * len(blocks)
+        if all(layout is not None for layout in layouts) and tensor_cores_requested():
+            host = bytearray(512 * len(blocks))
+            for i, layout in enumerate(layouts):
+                out = (ctypes.c_char * 512).from_buffer(host, 512 * i)
+                (gc, gcs), (gs, gss), (dc, dcs), (ds, dss) = layout
+                _abi.check(_abi.lib().ink_moe_stack_encode_banks(out, gc, gcs, gs, gss, dc, dcs, ds, dss, experts, hidden,
+                                                                 intermediate))
+            self.bank_maps = torch.frombuffer(host, dtype=torch.uint8).to(device)
+            assert self.bank_maps.data_ptr() % 128 == 0
+            maps_at = [self.bank_maps.data_ptr() + 512 * i for i in range(len(blocks))]
         raw = b"".join(struct.pack(
             _LAYER_FORMAT, ptr(b["router_weight"]), ptr(b["router_bias"]), ptr(b["global_scale"]), ptr(b["sources"]),
             ptr(b["shared_gate"]), ptr(b["shared_up"]), ptr(b["shared_down"]), ptr(b.get("norm_weight")),
-            ptr(b.get("topk_indices")), ptr(b.get("topk_weights")), ptr(b.get("gammas")), float(b["route_scale"]), 0)
-            for b in blocks)
+            ptr(b.get("topk_indices")), ptr(b.get("topk_weights")), ptr(b.get("gammas")), maps_at[i],
+            float(b["route_scale"]), 0)
+            for i, b in enumerate(blocks))
         self.table = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(device)
         size = _abi.lib().ink_moe_stack_scratch_bytes(self.n_layers, hidden, intermediate, experts, n_shared, top_k)
         self.scratch = torch.zeros(size, dtype=torch.uint8, device=device)   # counters start at zero, then only grow
@@ -66,7 +91,7 @@ class StackDescriptor:
             assert residual_io.numel() == normed_out.numel() == self.hidden
         _abi.require_cuda(x, partial_out, residual_io, normed_out)
         common = (self.table.data_ptr(), self.n_layers, x.data_ptr(), _abi.ptr(residual_io), _abi.ptr(normed_out),
-                  partial_out.data_ptr(), int(glue), float(eps), self.hidden, self.intermediate, self.experts,
+                  partial_out.data_ptr(), int(glue) | (2 if self.bank_maps is not None else 0), float(eps), self.hidden, self.intermediate, self.experts,
                   self.n_shared, self.top_k, self.scratch.data_ptr(), self.scratch.numel())
         if self.world == 1:
             _abi.check(_abi.lib().ink_moe_stack_decode(*common, self.status.data_ptr(), _abi.stream()))
@@ -86,13 +111,14 @@ class StackDescriptor:
 
     TRACE_SLOTS = ("layer_start", "router_rows_done", "shared_gate_up_done", "routed_gate_up_done",
                    "shared_gate_up_everywhere", "shared_down_done", "routed_gate_up_everywhere", "activations_staged",
-                   "routed_down_done", "down_everywhere", "norm_done", "", "producer_waits_for_routing",
-                   "producer_has_routing", "producer_layer_issued", "")
+                   "routed_down_done", "down_everywhere", "norm_done", "x_digits_written", "producer_waits_for_routing",
+                   "producer_has_routing", "producer_layer_issued", "x_digits_visible", "mma_gate_up_start", "mma_gate_up_end",
+                   "mma_down_start", "mma_down_end", "scales_gate_up_end", "scales_down_end", "", "")
 
     def trace(self) -> torch.Tensor:
         """Phase stamps of the last decode run with INKLING_STACK_TRACE=1: int64
-        [n_layers, 256, 16] nanoseconds (zero where a block did not stamp). Synchronises."""
+        [n_layers, 256, 24] nanoseconds (zero where a block did not stamp). Synchronises."""
         offset = _abi.lib().ink_moe_stack_trace_offset(self.n_layers, self.hidden, self.intermediate, self.experts,
                                                        self.n_shared, self.top_k)
-        raw = self.scratch[offset:offset + self.n_layers * 256 * 16 * 8].clone()
-        return raw.view(torch.int64).view(self.n_layers, 256, 16).cpu()
+        raw = self.scratch[offset:offset + self.n_layers * 256 * 24 * 8].clone()
+        return raw.view(torch.int64).view(self.n_layers, 256, 24).cpu()

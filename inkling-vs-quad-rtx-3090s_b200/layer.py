@@ -72,6 +72,12 @@ class ResidentExperts(nn.Module):
         i32 = dict(dtype=torch.int32, device=self.device)
         self.sources = torch.tensor([[weights[e][n].data_ptr() for n in names] for e in ids],
                                     dtype=torch.int64, device=self.device)
+        # banks of one kind evenly spaced in memory (one allocation per kind, say): (address of the first,
+        # byte distance) per kind, for the TMA descriptors of the one-launch kernel; otherwise None
+        self.bank_layout = self._even_spacing([[weights[e][n].data_ptr() for e in ids] for n in
+                                               ("gate_up_proj", "gate_up_proj_scale", "down_proj", "down_proj_scale")],
+                                              [first[n].numel() * first[n].element_size() for n in
+                                               ("gate_up_proj", "gate_up_proj_scale", "down_proj", "down_proj_scale")])
         self.resident = torch.ones(self.local, **i32)
         self.destinations = torch.zeros((0, self.stride), dtype=torch.int64, device=self.device)
         self.slot_experts = torch.full((0,), -1, **i32)
@@ -85,6 +91,18 @@ class ResidentExperts(nn.Module):
         self.counts = torch.empty(self.local, **i32)
         self.status = torch.zeros(1, **i32)
         self.capacity = 0
+
+    @staticmethod
+    def _even_spacing(addresses: list[list[int]], sizes: list[int]):
+        layout = []
+        for per_expert, size in zip(addresses, sizes):
+            stride = per_expert[1] - per_expert[0] if len(per_expert) > 1 else size
+            if stride < size or stride % 16 or per_expert[0] % 16:
+                return None
+            if any(b - a != stride for a, b in zip(per_expert, per_expert[1:])):
+                return None
+            layout.append((per_expert[0], stride))
+        return layout
 
     def _reserve(self, routes: int) -> None:
         if routes <= self.capacity:
@@ -173,7 +191,8 @@ class FusedMoE(nn.Module):
         return dict(router_weight=self.router_weight, router_bias=self.router_bias, global_scale=self.global_scale,
                     sources=ex.sources, shared_gate=self.shared_gate, shared_up=self.shared_up,
                     shared_down=self.shared_down, norm_weight=norm_weight, topk_indices=self.topk_indices,
-                    topk_weights=self.topk_weights, gammas=self.gammas, route_scale=self.route_scale)
+                    topk_weights=self.topk_weights, gammas=self.gammas, route_scale=self.route_scale,
+                    bank_layout=ex.bank_layout if ex.start == 0 else None)
 
     def world_size(self) -> int:
         group = _group_of(self.device_mesh)
