@@ -62,3 +62,18 @@ def test_bank_names_and_launch_syntax():
                                          "down_proj", "down_proj_scale", "down_proj_scale2"]
     assert k.expert_bank_names(False) == ["gate_up_proj", "down_proj"]
     assert callable(k.expert_plan[(1,)]) and callable(k.expert_copy[(128, 0)])
+
+
+def test_encode_banks_rejects_bad_arguments():
+    """ink_moe_stack_encode_banks validates on the host before it touches the driver: no GPU needed."""
+    import ctypes
+
+    from inkling_b200.kernels import _abi
+
+    lib = _abi.lib()
+    out = (ctypes.c_char * 512)()
+    # null output
+    assert lib.ink_moe_stack_encode_banks(None, 256, 1 << 20, 256, 1 << 17, 256, 1 << 20, 256, 1 << 17, 4, 1024, 512) != 0
+    # shapes that do not tile by 128 rows x 256 columns
+    assert lib.ink_moe_stack_encode_banks(out, 256, 1 << 20, 256, 1 << 17, 256, 1 << 20, 256, 1 << 17, 4, 1000, 512) != 0
+    assert b"tile" in lib.ink_last_error()
