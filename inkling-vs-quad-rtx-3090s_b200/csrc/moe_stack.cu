@@ -673,10 +673,7 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
       };
       // tensor-core variant: tell the waiters how far the issue has come (see tc_wait_issued)
       auto publish = [&]() {
-        if (tc) {
-          __threadfence_block();
-          sh.issued = issued;
-        }
+        if (tc) sh.issued = issued;
       };
       unsigned char* dst = nullptr;
       uint64_t* bar = nullptr;
@@ -901,7 +898,10 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
       const long long i = base + t;
       slot = (int)(i % kSStages);
       bool ok = !sh.failed;
-      if (tc && ok) ok = tc_wait_issued(i, &sh);   // the slot's previous tile may have been a tensor-core unit
+      if (tc) {   // the slot's previous tile may have been a tensor-core unit: one lane checks the issue count
+        if (ok && lane == 0) ok = tc_wait_issued(i, &sh);
+        ok = __all_sync(0xffffffffu, ok);
+      }
       if (ok) ok = mbar_wait(&sh.full[slot], (uint32_t)(i / kSStages) & 1);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
@@ -1417,7 +1417,8 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
       for (int i = 0; i < n_units; ++i) {
         const long long t = base + first_tile + 2 * i;
         const int slot = (int)(t % kSStages), sfs = (int)(qseq % kTcSfSlots);
-        bool ok = tc_wait_issued(t, &sh) && tc_wait(&sh.full[slot], (uint32_t)(t / kSStages) & 1u, &sh);
+        bool ok = lane != 0 || tc_wait_issued(t, &sh);   // one lane polls the issue count
+        ok = __all_sync(0xffffffffu, ok) && tc_wait(&sh.full[slot], (uint32_t)(t / kSStages) & 1u, &sh);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         // lane = row % 32, column = row / 32, four scale bytes (one 64-column MMA step) per column
@@ -1482,22 +1483,22 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
           int index;
           const int parts = tc_split((long long)tg * S::GU_CHUNKS, (long long)tg * S::GU_CHUNKS + S::GU_CHUNKS - 1, total,
                                      gridDim.x, blockIdx.x, &index);
+          // A split tile is finished by the block that holds its first units: that block reaches the tile
+          // last (end of its range), the others first (start of theirs), so their parts are long there.
           bool finish = true;
           if (parts > 1) {
             float* part = a.gu_part + (size_t)tg * S::GU_CHUNKS * kTcRows;
-            part[(size_t)index * kTcRows + row] = sum;
-            __threadfence();   // every writer pushes its own store out before the count moves
-            epilogue_sync();
-            if (et == 0) {
+            if (index > 0) {
+              part[(size_t)index * kTcRows + row] = sum;
+              __threadfence();   // every writer pushes its own store out before the count moves
+              epilogue_sync();
+              if (et == 0) red_release_add(tile_count + tg, 1u);
+              finish = false;
+            } else {
+              if (et == 0) wait_global(tile_count + tg, epoch1 * (unsigned)(parts - 1), &sh);
+              epilogue_sync();
               __threadfence();
-              sh.finisher = atomicAdd(tile_count + tg, 1u) + 1u == epoch1 * (unsigned)parts;
-            }
-            epilogue_sync();
-            finish = sh.finisher != 0;
-            if (finish) {
-              __threadfence();
-              sum = 0.f;
-              for (int p = 0; p < parts; ++p) sum += __ldcg(part + (size_t)p * kTcRows + row);   // fixed order
+              for (int p = 1; p < parts; ++p) sum += __ldcg(part + (size_t)p * kTcRows + row);   // fixed order
             }
           }
           if (finish) {

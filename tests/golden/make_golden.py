@@ -1,7 +1,7 @@
 """Generates tests/golden/golden.npz by RUNNING THE REFERENCE on seeded inputs.
 
-Needs the reference checkout (default /root/reference) and therefore only runs on the
-development machine; the fixtures it writes travel with the repository.
+Needs a checkout of the reference (first argument, or the default of REFERENCE below) and
+therefore only runs where one is mounted; the fixtures it writes travel with the repository.
 
 Three sources, all the reference's own code:
   A. its PyTorch classes (my_inkling/model.py): MyInklingTopkRouter,
