@@ -63,12 +63,11 @@ __device__ __forceinline__ float bf16_to_f32(uint32_t bits16) { return __uint_as
 __device__ __forceinline__ float bf16lo(uint32_t packed) { return __uint_as_float(packed << 16); }
 __device__ __forceinline__ float bf16hi(uint32_t packed) { return __uint_as_float(packed & 0xffff0000u); }
 
-// round to nearest even, NaN kept quiet: what a cast to BF16 does
+// round to nearest even: what a cast to BF16 does (one instruction; a NaN becomes the canonical BF16 NaN)
 __device__ __forceinline__ uint32_t f32_to_bf16_bits(float v) {
-  uint32_t bits = __float_as_uint(v);
-  if ((bits & 0x7fffffffu) > 0x7f800000u) return (bits >> 16) | 0x40u;
-  bits += 0x7fffu + ((bits >> 16) & 1u);
-  return bits >> 16;
+  uint16_t r;
+  asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(r) : "f"(v));
+  return r;
 }
 __device__ __forceinline__ float round_bf16(float v) { return bf16_to_f32(f32_to_bf16_bits(v)); }
 
