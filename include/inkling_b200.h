@@ -210,7 +210,8 @@ int ink_expert_reduce(const void* down, const int64_t* indices, const void* weig
  *               With bank_maps set in every layer the routed experts run on the tensor cores
  *               (tcgen05.mma kind::mxf4nvf4 on the packed codes and their block scales, no
  *               conversion); with null in every layer they run on the CUDA cores.
- *  x            BF16 [hidden]: input of the first block
+ *  x            BF16 [hidden]: input of the first block (x, residual_io, normed_out, partial_out and every
+ *               layer's norm_weight are read and written 16 bytes at a time: 16-byte aligned)
  *  glue = 0     n_layers must be 1; partial_out FP32 [hidden] receives the block's output
  *  glue = 1     residual_io BF16 [hidden] is the residual stream (updated in place),
  *               normed_out BF16 [hidden] the normalised output after the last block,

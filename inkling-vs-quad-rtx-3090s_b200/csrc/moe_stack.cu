@@ -426,23 +426,36 @@ __device__ void stack_router_tail(const StackArgs& a, const StackLayer& ly, int 
 }
 
 // ---------------------------------------------------------------- x staging (consumers)
-// All consumer threads: `value` holds this thread's elements i = ct + n * (kSC*32) of the
-// new activation vector (already BF16-rounded, as FP32). Writes BF16 and normalised FP16.
+// The activation vector between blocks lives in the consumer threads as groups of eight
+// consecutive elements (packed BF16, 16 bytes): thread ct holds the groups g * VT + ct,
+// g < VG, of the D / 8 groups; threads ct >= VT hold nothing (hidden sizes below 2048).
 template <int D>
-__device__ __forceinline__ void stage_x(uint16_t* s_x16, uint16_t* s_xbf, const float (&value)[(D + kSC * 32 - 1) / (kSC * 32)],
-                                        float amax_bound, StackShared* sh, int ct) {
+struct VecShape {
+  static constexpr int VG = D >= 2048 ? D / 2048 : 1;
+  static constexpr int VT = D / 8 / VG;
+  static_assert(VT % 32 == 0 && VT <= kSC * 32, "whole warps hold the vector");
+};
+
+// CUDA-core variant: BF16 copy and a copy normalised by a power of two into FP16.
+template <int D>
+__device__ __forceinline__ void stage_x(uint16_t* s_x16, uint16_t* s_xbf, const uint4 (&xb)[VecShape<D>::VG], float amax_bound,
+                                        StackShared* sh, int ct) {
+  using V = VecShape<D>;
   // power-of-two normaliser from an upper bound of the largest magnitude
   float inverse;
   const uint32_t bits = f32_to_bf16_bits(amax_bound) & 0x7fffu;
   const float scale = pow2_normaliser(bits + 0x80u > 0x7f7fu ? 0x7f7fu : bits + 0x80u, &inverse);  // one binade of margin
-  constexpr int PER = (D + kSC * 32 - 1) / (kSC * 32);
+  if (ct < V::VT) {
 #pragma unroll
-  for (int n = 0; n < PER; ++n) {
-    const int i = ct + n * (kSC * 32);
-    if (i < D) {
-      s_xbf[i] = (uint16_t)f32_to_bf16_bits(value[n]);
-      const uint32_t h2 = f32x2_to_f16x2(value[n] * scale, 0.f);
-      s_x16[i] = (uint16_t)(h2 & 0xffffu);
+    for (int g = 0; g < V::VG; ++g) {
+      const int group = g * V::VT + ct;
+      reinterpret_cast<uint4*>(s_xbf)[group] = xb[g];
+      uint4 h;
+      h.x = f32x2_to_f16x2(bf16lo(xb[g].x) * scale, bf16hi(xb[g].x) * scale);
+      h.y = f32x2_to_f16x2(bf16lo(xb[g].y) * scale, bf16hi(xb[g].y) * scale);
+      h.z = f32x2_to_f16x2(bf16lo(xb[g].z) * scale, bf16hi(xb[g].z) * scale);
+      h.w = f32x2_to_f16x2(bf16lo(xb[g].w) * scale, bf16hi(xb[g].w) * scale);
+      reinterpret_cast<uint4*>(s_x16)[group] = h;
     }
   }
   if (ct == 0) sh->x_inverse = inverse;
@@ -500,23 +513,22 @@ __device__ __forceinline__ int tc_split(long long first, long long last, long lo
 }
 
 // Tensor-core variant: the same vector as BF16 (router, shared experts) and as four E2M1 digit rows
-// in the swizzled N-operand layout, block scales to `sh->sfbx`. All consumer threads. The digit rows
-// are made from the BF16 copy in a short rolled loop: this runs once per layer, and straight-line code
-// for sixteen elements per thread costs more in instruction fetch than in arithmetic.
+// in the swizzled N-operand layout, block scales to `sh->sfbx`. Whole warps of holders call it.
 template <int D>
-__device__ __forceinline__ void stage_x_tc(unsigned char* s_xdig, uint16_t* s_xbf, const float (&value)[(D + kSC * 32 - 1) / (kSC * 32)],
-                                           float amax_bound, StackShared* sh, int ct) {
+__device__ __forceinline__ void stage_x_tc(unsigned char* s_xdig, uint16_t* s_xbf, const uint4 (&xb)[VecShape<D>::VG], float amax_bound,
+                                           StackShared* sh, int ct) {
+  using V = VecShape<D>;
   float inverse;
   const uint32_t bits = f32_to_bf16_bits(amax_bound) & 0x7fffu;
   const float scale = 512.f * pow2_normaliser(bits + 0x80u > 0x7f7fu ? 0x7f7fu : bits + 0x80u, &inverse);  // below 1024
-  constexpr int PER = D / (kSC * 32);
-  static_assert(D % (kSC * 32) == 0, "every thread stages whole blocks' worth of elements");
-#pragma unroll
-  for (int n = 0; n < PER; ++n) s_xbf[ct + n * (kSC * 32)] = (uint16_t)f32_to_bf16_bits(value[n]);
-  consumer_sync();
+  if (ct < V::VT) {
 #pragma unroll 1
-  for (int g = ct; g < D / 8; g += kSC * 32)
-    tc_stage8(reinterpret_cast<const uint4*>(s_xbf)[g], scale, s_xdig, 8, 0, g * 8, &sh->sfbx[0][0], 256);
+    for (int g = 0; g < V::VG; ++g) {
+      const int group = g * V::VT + ct;
+      reinterpret_cast<uint4*>(s_xbf)[group] = xb[g];
+      tc_stage8(xb[g], scale, s_xdig, 8, 0, group * 8, &sh->sfbx[0][0], 256);
+    }
+  }
   if (ct == 0) sh->x_inverse = inverse * (1.f / 512.f);
 }
 
@@ -889,7 +901,8 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
   } else if (warp <= kSC) {
     // =========================================================== consumers
     const int cw = warp - 1, ct = threadIdx.x - 32;
-    constexpr int PER = (D + kSC * 32 - 1) / (kSC * 32);
+    constexpr int VG = VecShape<D>::VG, VT = VecShape<D>::VT;   // groups of eight elements per thread, threads that hold some
+    const bool holder = ct < VT;
     long long base = 0;   // index of this layer's first tile in the block's whole sequence
 
     // first tile index >= start that belongs to this consumer (tile t belongs to consumer t % kSC)
@@ -933,12 +946,12 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
 
     const int sub = warp & 3;   // the tensor-memory subpartition this warp can reach
     // stages the next activation vector for the gate/up phases; `ready` = layers staged once this returns
-    auto stage = [&](const float (&value)[PER], float amax_bound, int ready) {
+    auto stage = [&](const uint4 (&xb)[VG], float amax_bound, int ready) {
       if (!tc) {
-        stage_x<D>(s_x16, s_xbf, value, amax_bound, &sh, ct);
+        stage_x<D>(s_x16, s_xbf, xb, amax_bound, &sh, ct);
         return;
       }
-      stage_x_tc<D>(s_xdig, s_xbf, value, amax_bound, &sh, ct);
+      stage_x_tc<D>(s_xdig, s_xbf, xb, amax_bound, &sh, ct);
       if (ct == 0 && ready >= 2) INK_TRACE(ready - 2, kTrXDigits);
       tc_proxy_fence();   // the digit rows are read by the tensor core
       consumer_sync();
@@ -953,21 +966,23 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
 
     // ---- first activation vector
     {
-      float value[PER];
-      float amax = 0.f;
+      uint4 xb[VG];
+      uint32_t amax_bits = 0;
 #pragma unroll
-      for (int n = 0; n < PER; ++n) {
-        const int i = ct + n * (kSC * 32);
-        value[n] = i < D ? bf16_to_f32(a.x[i]) : 0.f;
-        amax = fmaxf(amax, fabsf(value[n]));
+      for (int g = 0; g < VG; ++g) {
+        xb[g] = holder ? reinterpret_cast<const uint4*>(a.x)[g * VT + ct] : make_uint4(0, 0, 0, 0);
+        const uint32_t w4[4] = {xb[g].x, xb[g].y, xb[g].z, xb[g].w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) amax_bits = max(amax_bits, max(w4[k] & 0x7fffu, (w4[k] >> 16) & 0x7fffu));
       }
+      float amax = bf16_to_f32(amax_bits);
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
       if (lane == 0) sh.red[cw][0] = amax;
       consumer_sync();
       amax = 0.f;
       for (int w = 0; w < kSC; ++w) amax = fmaxf(amax, sh.red[w][0]);
-      stage(value, amax, 1);
+      stage(xb, amax, 1);
       consumer_sync();
     }
 
@@ -1205,7 +1220,7 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
       if (tracer) INK_TRACE(layer, kTrRtGuAll);
       if (!sh.failed) {
         for (int job = cw; job < a.top_k; job += kSC) {
-          const float inverse = warp_stage_f16(a.activated + ((size_t)par * a.top_k + job) * F, s_act + (size_t)job * F, F, lane);
+          const float inverse = warp_stage_f16<F>(a.activated + ((size_t)par * a.top_k + job) * F, s_act + (size_t)job * F, lane);
           if (lane == 0) sh.inverse[job] = inverse;
         }
       }
@@ -1316,47 +1331,63 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
       // completed) and is needed clean by the next layer
       if (tc && blockIdx.x == 0 && ct < kSMaxTopK) a.act_amax[((layer + 1) & 1) * kSMaxTopK + ct] = 0u;
       // ------------------------------------------------ residual add + RMS norm (every block, redundantly)
-      float value[PER];
       {
         const uint16_t* res_in = a.residual + (size_t)par * D;
         uint16_t* res_out = a.residual + (size_t)(par ^ 1) * D;
         float sumsq = 0.f, amax_h = 0.f, amax_w = 0.f;
-        // all loads first (they are independent), arithmetic after: one L2 round trip, not PER
-        const bool live = !sh.failed;
+        // all loads first (they are independent), arithmetic after: one L2 round trip; 16-byte loads of eight
+        // consecutive elements keep both the loads and the code that follows short
+        const bool live = !sh.failed && holder;
         const int world = a.world;
-        uint16_t res[PER], nw[PER];
-        float part[PER];
+        uint4 res[VG], nw[VG];
+        float part[VG][8];
 #pragma unroll
-        for (int n = 0; n < PER; ++n) {
-          const int i = ct + n * (kSC * 32);
-          const bool ok = live && i < D;
-          res[n] = ok ? __ldcg(res_in + i) : (uint16_t)0;
-          nw[n] = ok ? norm_weight[i] : (uint16_t)0;
-          part[n] = 0.f;
+        for (int g = 0; g < VG; ++g) {
+          const int group = g * VT + ct;
+          res[g] = live ? __ldcg(reinterpret_cast<const uint4*>(res_in) + group) : make_uint4(0, 0, 0, 0);
+          nw[g] = live ? reinterpret_cast<const uint4*>(norm_weight)[group] : make_uint4(0, 0, 0, 0);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) part[g][k] = 0.f;
         }
-        // every rank's delivery, summed in rank order (same bits on every rank); one rank at a time so that
-        // a rank's loads are all in flight together without holding world x PER registers
+        // every rank's delivery, summed in rank order (same bits on every rank)
         for (int r = 0; r < world; ++r) {
-          float got[PER];
+          float4 got[VG][2];
 #pragma unroll
-          for (int n = 0; n < PER; ++n) {
-            const int i = ct + n * (kSC * 32);
-            got[n] = (live && i < D) ? __ldcg(inbox + (size_t)r * D + i) : 0.f;
+          for (int g = 0; g < VG; ++g) {
+            const float4* src = reinterpret_cast<const float4*>(inbox + (size_t)r * D) + (size_t)(g * VT + ct) * 2;
+            got[g][0] = live ? __ldcg(src) : make_float4(0.f, 0.f, 0.f, 0.f);
+            got[g][1] = live ? __ldcg(src + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
           }
 #pragma unroll
-          for (int n = 0; n < PER; ++n) part[n] += got[n];
+          for (int g = 0; g < VG; ++g) {
+            part[g][0] += got[g][0].x; part[g][1] += got[g][0].y; part[g][2] += got[g][0].z; part[g][3] += got[g][0].w;
+            part[g][4] += got[g][1].x; part[g][5] += got[g][1].y; part[g][6] += got[g][1].z; part[g][7] += got[g][1].w;
+          }
         }
+        float h[VG][8];
 #pragma unroll
-        for (int n = 0; n < PER; ++n) {
-          const int i = ct + n * (kSC * 32);
-          const float h = round_bf16(bf16_to_f32(res[n]) + round_bf16(part[n]));
-          value[n] = h;
-          sumsq = fmaf(h, h, sumsq);
-          amax_h = fmaxf(amax_h, fabsf(h));
-          amax_w = fmaxf(amax_w, fabsf(bf16_to_f32(nw[n])));
-          if (blockIdx.x == 0 && live && i < D) {
-            res_out[i] = (uint16_t)f32_to_bf16_bits(h);
-            if (layer + 1 == a.n_layers) a.partial[i] = part[n];
+        for (int g = 0; g < VG; ++g) {
+          const uint32_t r4[4] = {res[g].x, res[g].y, res[g].z, res[g].w}, w4[4] = {nw[g].x, nw[g].y, nw[g].z, nw[g].w};
+          uint32_t packed[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float lo = round_bf16(bf16lo(r4[k]) + round_bf16(part[g][2 * k]));
+            const float hi = round_bf16(bf16hi(r4[k]) + round_bf16(part[g][2 * k + 1]));
+            h[g][2 * k] = lo;
+            h[g][2 * k + 1] = hi;
+            sumsq = fmaf(lo, lo, fmaf(hi, hi, sumsq));
+            amax_h = fmaxf(amax_h, fmaxf(fabsf(lo), fabsf(hi)));
+            amax_w = fmaxf(amax_w, fmaxf(fabsf(bf16lo(w4[k])), fabsf(bf16hi(w4[k]))));
+            packed[k] = f32_to_bf16_bits(lo) | (f32_to_bf16_bits(hi) << 16);
+          }
+          if (blockIdx.x == 0 && live) {
+            const int group = g * VT + ct;
+            reinterpret_cast<uint4*>(res_out)[group] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            if (layer + 1 == a.n_layers) {
+              float4* out = reinterpret_cast<float4*>(a.partial) + (size_t)group * 2;
+              out[0] = make_float4(part[g][0], part[g][1], part[g][2], part[g][3]);
+              out[1] = make_float4(part[g][4], part[g][5], part[g][6], part[g][7]);
+            }
           }
         }
 #pragma unroll
@@ -1380,21 +1411,26 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
           amax_w = fmaxf(amax_w, sh.red[w][2]);
         }
         const float scale = rsqrtf(sumsq / (float)D + a.eps);
+        uint4 xb[VG];
 #pragma unroll
-        for (int n = 0; n < PER; ++n) {
-          const int i = ct + n * (kSC * 32);
-          if (i < D) value[n] = round_bf16(round_bf16(value[n] * scale) * bf16_to_f32(nw[n]));
+        for (int g = 0; g < VG; ++g) {
+          const uint32_t w4[4] = {nw[g].x, nw[g].y, nw[g].z, nw[g].w};
+          uint32_t packed[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float lo = round_bf16(h[g][2 * k] * scale) * bf16lo(w4[k]);
+            const float hi = round_bf16(h[g][2 * k + 1] * scale) * bf16hi(w4[k]);
+            packed[k] = f32_to_bf16_bits(lo) | (f32_to_bf16_bits(hi) << 16);
+          }
+          xb[g] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
         }
         if (layer + 1 == a.n_layers) {
-          if (blockIdx.x == 0) {
+          if (blockIdx.x == 0 && live) {
 #pragma unroll
-            for (int n = 0; n < PER; ++n) {
-              const int i = ct + n * (kSC * 32);
-              if (i < D) a.normed_out[i] = (uint16_t)f32_to_bf16_bits(value[n]);
-            }
+            for (int g = 0; g < VG; ++g) reinterpret_cast<uint4*>(a.normed_out)[g * VT + ct] = xb[g];
           }
         } else {
-          stage(value, amax_h * scale * amax_w, layer + 2);
+          stage(xb, amax_h * scale * amax_w, layer + 2);
           // contributions of inactive routes must read as zero in the next layer too
           for (int i = ct; i < (kSMaxTopK + kSMaxShared) * kSMaxRows; i += kSC * 32) (&sh.contrib[0][0])[i] = 0.f;
           if (ct < 3) sh.done[par ^ 1][ct] = 0;
@@ -1761,7 +1797,8 @@ static int stack_decode(const void* layers, int n_layers, const void* x, void* r
               "moe_stack: rank=%d world=%d", rank, world);
   INK_REQUIRE(scratch_bytes >= ink_moe_stack_scratch_bytes(n_layers, hidden, intermediate, experts, n_shared, top_k),
               kBadArgument, "moe_stack: scratch of %zu bytes is too small", scratch_bytes);
-  INK_REQUIRE(aligned16(x) && aligned16(scratch) && aligned16(partial_out), kMisaligned, "moe_stack: misaligned buffer");
+  INK_REQUIRE(aligned16(x) && aligned16(scratch) && aligned16(partial_out) && aligned16(residual_io) && aligned16(normed_out),
+              kMisaligned, "moe_stack: misaligned buffer (x, scratch, partial, residual and normed need 16-byte alignment)");
   StackArgs a;
   a.layers = (const StackLayer*)layers;
   a.n_layers = n_layers;

@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gate_up_stream_kernel(Decod
     const int cw = warp - 1;
     const uint16_t* x = a.x + (size_t)token * K;
     if (cw == 0) {
-      const float inverse = warp_stage_f16(x, s_x16, K, lane);
+      const float inverse = warp_stage_f16<K>(x, s_x16, lane);
       if (lane == 0) s_inverse = inverse;
     }
     for (int i = threadIdx.x - 32; i < K / 8; i += kConsumers * 32)
@@ -323,8 +323,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) down_stream_kernel(DecodeAr
     const int cw = warp - 1;
     for (int job = cw; job < jobs; job += kConsumers) {
       if (job < a.top_k) {
-        const float inverse = warp_stage_f16(a.activated + (size_t)(token * a.top_k + job) * K,
-                                             s_act + (size_t)job * K, K, lane);
+        const float inverse = warp_stage_f16<K>(a.activated + (size_t)(token * a.top_k + job) * K,
+                                                s_act + (size_t)job * K, lane);
         if (lane == 0) s_job[job].scale *= inverse;
       } else {
         const int e = job - a.top_k;

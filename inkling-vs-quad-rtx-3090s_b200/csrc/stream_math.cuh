@@ -72,20 +72,34 @@ __device__ __forceinline__ bool reduced_owner(int lane) {  // one lane per row
   return (lane & ((32 / R) - 1)) == 0;
 }
 
-// One warp: K BF16 values -> FP16 scaled by a power of two into [1, 2); returns the inverse.
-__device__ __forceinline__ float warp_stage_f16(const uint16_t* src, uint16_t* dst, int k, int lane) {
+// One warp: K BF16 values written by other blocks (read through L2, never from a stale L1 line)
+// -> FP16 scaled by a power of two into [1, 2); returns the inverse. One round trip: every lane
+// loads its K / 256 groups of eight values at once and keeps them for the second pass.
+template <int K>
+__device__ __forceinline__ float warp_stage_f16(const uint16_t* src, uint16_t* dst, int lane) {
+  constexpr int N = K / 256;
+  static_assert(K % 256 == 0, "a warp stages whole rounds of 32 x 8 values");
+  uint4 v[N];
   uint32_t amax = 0;
-  for (int i = lane; i < k / 2; i += 32) {
-    const uint32_t v = reinterpret_cast<const uint32_t*>(src)[i];
-    amax = max(amax, max(v & 0x7fffu, (v >> 16) & 0x7fffu));
+#pragma unroll
+  for (int n = 0; n < N; ++n) {
+    v[n] = __ldcg(reinterpret_cast<const uint4*>(src) + n * 32 + lane);
+    const uint32_t w4[4] = {v[n].x, v[n].y, v[n].z, v[n].w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) amax = max(amax, max(w4[k] & 0x7fffu, (w4[k] >> 16) & 0x7fffu));
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, o));
   float inverse;
   const float scale = pow2_normaliser(amax, &inverse);
-  for (int i = lane; i < k / 2; i += 32) {
-    const uint32_t v = reinterpret_cast<const uint32_t*>(src)[i];
-    reinterpret_cast<uint32_t*>(dst)[i] = f32x2_to_f16x2(bf16lo(v) * scale, bf16hi(v) * scale);
+#pragma unroll
+  for (int n = 0; n < N; ++n) {
+    uint4 h;
+    h.x = f32x2_to_f16x2(bf16lo(v[n].x) * scale, bf16hi(v[n].x) * scale);
+    h.y = f32x2_to_f16x2(bf16lo(v[n].y) * scale, bf16hi(v[n].y) * scale);
+    h.z = f32x2_to_f16x2(bf16lo(v[n].z) * scale, bf16hi(v[n].z) * scale);
+    h.w = f32x2_to_f16x2(bf16lo(v[n].w) * scale, bf16hi(v[n].w) * scale);
+    reinterpret_cast<uint4*>(dst)[n * 32 + lane] = h;
   }
   return inverse;
 }
