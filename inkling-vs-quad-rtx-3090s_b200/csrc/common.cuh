@@ -145,7 +145,7 @@ __device__ __forceinline__ float silu_mul(float gate, float up) { return gate / 
 // inverse 2^e is returned through `inverse`.
 __device__ __forceinline__ float pow2_normaliser(uint32_t amax_bits, float* inverse) {
   int field = (int)((amax_bits >> 7) & 0xffu);
-  field = field < 1 ? 127 : (field > 253 ? 253 : field);
+  field = field < 1 ? 127 : (field > 253 ? 253 : (field < 16 ? 16 : field));   // the multiplier stays below 2^112: callers scale it further
   if (amax_bits == 0) field = 127;
   *inverse = __uint_as_float((uint32_t)field << 23);
   return __uint_as_float((uint32_t)(254 - field) << 23);

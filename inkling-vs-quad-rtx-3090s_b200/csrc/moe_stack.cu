@@ -250,6 +250,8 @@ struct StackShared {
   int done[2][3];                       // tiles finished per layer parity: shared g/u, routed g/u, down
   unsigned epoch1;                      // launches completed before this one, plus one: scales every target
   volatile int routed_layers;           // layers whose routing table is in `routes` (set by the auxiliary warp)
+  volatile int sact_flag[kSMaxShared];  // layers whose shared-expert activations are staged, per shared expert
+  volatile int act_flag[kSMaxTopK];     // layers whose routed activations are staged, per route
   volatile int failed;
   // tensor-core path
   uint64_t sf_full[kTcSfSlots], sf_empty[kTcSfSlots];   // weight scales of a unit are in tensor memory / may be overwritten
@@ -337,6 +339,17 @@ __device__ __forceinline__ bool wait_routing(int layer, StackShared* sh) {
   }
   __threadfence_block();
   return true;
+}
+
+// Bounded wait of a warp until a staging flag of this block has reached `layer + 1` (one lane polls).
+__device__ __forceinline__ void wait_flag(volatile int* flag, int layer, StackShared* sh, int lane) {
+  if (lane == 0 && *flag <= layer) {
+    const long long t0 = clock64();
+    while (*flag <= layer && !sh->failed)
+      if (clock64() - t0 > kWaitLimitCycles) sh->failed = 1;
+  }
+  __syncwarp();
+  __threadfence_block();
 }
 
 __device__ __forceinline__ void consumer_sync() {
@@ -450,11 +463,7 @@ __device__ __forceinline__ void stage_x(uint16_t* s_x16, uint16_t* s_xbf, const 
     for (int g = 0; g < V::VG; ++g) {
       const int group = g * V::VT + ct;
       reinterpret_cast<uint4*>(s_xbf)[group] = xb[g];
-      uint4 h;
-      h.x = f32x2_to_f16x2(bf16lo(xb[g].x) * scale, bf16hi(xb[g].x) * scale);
-      h.y = f32x2_to_f16x2(bf16lo(xb[g].y) * scale, bf16hi(xb[g].y) * scale);
-      h.z = f32x2_to_f16x2(bf16lo(xb[g].z) * scale, bf16hi(xb[g].z) * scale);
-      h.w = f32x2_to_f16x2(bf16lo(xb[g].w) * scale, bf16hi(xb[g].w) * scale);
+      const uint4 h = stage_pack8(xb[g], scale);
       reinterpret_cast<uint4*>(s_x16)[group] = h;
     }
   }
@@ -629,6 +638,8 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
     sh.sg_done = 0;
     sh.issued = 0;
     sh.routed_layers = 0;
+    for (int i = 0; i < kSMaxShared; ++i) sh.sact_flag[i] = 0;
+    for (int i = 0; i < kSMaxTopK; ++i) sh.act_flag[i] = 0;
     sh.failed = 0;
     sh.epoch1 = *a.epoch + 1u;
     for (int i = 0; i < 6; ++i) (&sh.done[0][0])[i] = 0;
@@ -1140,8 +1151,11 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
         }
       }
       if (tracer) INK_TRACE(layer, kTrRtGuDone);
-      // every consumer of this block is past its gate/up tiles: x staging may be overwritten
-      consumer_sync();
+      // The phases that follow are not separated by block-wide barriers: a warp that is done with its gate/up
+      // tiles goes on with its down tiles, and waits only for the staging flag of the vector it needs. Only
+      // where the shared experts' staging area overlaps the x staging (narrow experts) must every warp be
+      // past its gate/up tiles first.
+      if (!tc && kSMaxTopK * F * 2 < D * 4) consumer_sync();
       // ------------------------------------------------ shared down
       if (lane == 0) {
         wait_global(sync + kShGuDone, epoch1 * gridDim.x, &sh);
@@ -1149,18 +1163,32 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
       }
       __syncwarp();
       if (tracer) INK_TRACE(layer, kTrShGuAll);
-      if (!sh.failed) {
-        for (int e = cw; e < a.n_shared; e += kSC) {
-          const uint16_t* src = a.shared_activated + ((size_t)par * a.n_shared + e) * F;
+      for (int e = cw; e < a.n_shared; e += kSC) {   // warp e stages shared expert e: act * gamma, BF16
+        if (!sh.failed) {
+          const uint4* src = reinterpret_cast<const uint4*>(a.shared_activated + ((size_t)par * a.n_shared + e) * F);
           const float gamma = sh.routes[par].gamma[e];
-          uint32_t* dst = reinterpret_cast<uint32_t*>(s_sact + (size_t)e * F);
-          for (int i = lane; i < F / 2; i += 32) {
-            const uint32_t v = __ldcg(reinterpret_cast<const uint32_t*>(src) + i);
-            dst[i] = f32_to_bf16_bits(bf16lo(v) * gamma) | (f32_to_bf16_bits(bf16hi(v) * gamma) << 16);
+          uint4* dst = reinterpret_cast<uint4*>(s_sact + (size_t)e * F);
+          constexpr int N = F / 256;
+          uint4 v[N];
+#pragma unroll
+          for (int n = 0; n < N; ++n) v[n] = __ldcg(src + n * 32 + lane);
+#pragma unroll
+          for (int n = 0; n < N; ++n) {
+            uint4 o;
+            o.x = f32_to_bf16_bits(bf16lo(v[n].x) * gamma) | (f32_to_bf16_bits(bf16hi(v[n].x) * gamma) << 16);
+            o.y = f32_to_bf16_bits(bf16lo(v[n].y) * gamma) | (f32_to_bf16_bits(bf16hi(v[n].y) * gamma) << 16);
+            o.z = f32_to_bf16_bits(bf16lo(v[n].z) * gamma) | (f32_to_bf16_bits(bf16hi(v[n].z) * gamma) << 16);
+            o.w = f32_to_bf16_bits(bf16lo(v[n].w) * gamma) | (f32_to_bf16_bits(bf16hi(v[n].w) * gamma) << 16);
+            dst[n * 32 + lane] = o;
           }
         }
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence_block();
+          sh.sact_flag[e] = layer + 1;
+        }
       }
-      consumer_sync();
+      unsigned sact_seen = 0;
       for (int t = first_of(plan.s_sd); t < plan.s_qd; t += kSC) {
         const unsigned char* src;
         int slot;
@@ -1173,6 +1201,10 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
         const int per_e = plan.n_g * S::SD_PER_GROUP;
         const int e = i / per_e, rem = i % per_e;
         const int local0 = (rem / S::SD_PER_GROUP) * S::RT + (rem % S::SD_PER_GROUP) * S::SD_ROWS;
+        if (!((sact_seen >> e) & 1u)) {   // once per layer and shared expert
+          wait_flag(&sh.sact_flag[e], layer, &sh, lane);
+          sact_seen |= 1u << e;
+        }
         const uint4* xs = reinterpret_cast<const uint4*>(s_sact + (size_t)e * F);
 #pragma unroll 1
         for (int row = 0; row < S::SD_ROWS; ++row) {
@@ -1218,13 +1250,17 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
       if (lane == 0) wait_global(sync + kRtGuDone, rt_gu_target, &sh);
       __syncwarp();
       if (tracer) INK_TRACE(layer, kTrRtGuAll);
-      if (!sh.failed) {
-        for (int job = cw; job < a.top_k; job += kSC) {
+      for (int job = cw; job < a.top_k; job += kSC) {   // warp j stages route j
+        if (!sh.failed) {
           const float inverse = warp_stage_f16<F>(a.activated + ((size_t)par * a.top_k + job) * F, s_act + (size_t)job * F, lane);
           if (lane == 0) sh.inverse[job] = inverse;
         }
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence_block();
+          sh.act_flag[job] = layer + 1;
+        }
       }
-      consumer_sync();
       if (tracer) INK_TRACE(layer, kTrActStaged);
       {
         const int sl = lane % S::LPR, rp = lane / S::LPR;
@@ -1241,6 +1277,7 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
           if (r.dn_codes) {
             if (loaded != choice) {
               loaded = choice;
+              wait_flag(&sh.act_flag[choice], layer, &sh, lane);
 #pragma unroll
               for (int j = 0; j < S::QD_CPL; ++j) {
                 const uint4* p4 = reinterpret_cast<const uint4*>(s_act + (size_t)choice * F + (j * S::LPR + sl) * 32);
