@@ -1130,20 +1130,26 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
           if (r.gu_codes) {
             const float scale = r.gu_scale2 * x_inverse;
             uint16_t* y = a.activated + ((size_t)par * a.top_k + choice) * F + row0 / 2;
-            float gate = 0.f;
-#pragma unroll 1
-            for (int row = 0; row < S::QG_ROWS; ++row) {   // even rows are gate, odd rows up
+            // every lane accumulates its columns of all rows of the tile, then ONE multi-row reduction
+            // (QG_ROWS/2 + ... shuffles instead of five per row) leaves row r's total in its owner lane
+            float acc[S::QG_ROWS];
+#pragma unroll
+            for (int row = 0; row < S::QG_ROWS; ++row) {
               const unsigned char* codes = src + (size_t)row * (D / 2) + lane * 16;
               const unsigned char* scales = src + S::QG_CODES + (size_t)row * (D / 16) + lane * 2;
-              float acc = 0.f;
+              float sum = 0.f;
 #pragma unroll
               for (int j = 0; j < S::QG_CPL; ++j)
-                acc += dot32(*reinterpret_cast<const uint4*>(codes + j * 512), *reinterpret_cast<const uint16_t*>(scales + j * 64), xr[j]);
-              acc = warp_sum(acc) * scale;
-              if ((row & 1) == 0) gate = acc;
-              else if (lane == 0) y[row >> 1] = (uint16_t)f32_to_bf16_bits(silu_mul(gate, acc));
+                sum += dot32(*reinterpret_cast<const uint4*>(codes + j * 512), *reinterpret_cast<const uint16_t*>(scales + j * 64), xr[j]);
+              acc[row] = sum;
             }
             release(slot);
+            const float mine = multi_reduce<S::QG_ROWS>(acc, lane) * scale;
+            // even rows are gate, odd rows up: the owner of an even row fetches the odd row next to it
+            constexpr int kOwnerStride = 32 / S::QG_ROWS;
+            const float up = __shfl_down_sync(0xffffffffu, mine, kOwnerStride);
+            const int row = reduced_row<S::QG_ROWS>(lane);
+            if (reduced_owner<S::QG_ROWS>(lane) && (row & 1) == 0) y[row >> 1] = (uint16_t)f32_to_bf16_bits(silu_mul(mine, up));
           } else {
             release(slot);
           }
@@ -1289,21 +1295,42 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
               }
             }
             const float scale = r.dn_scale2 * sh.inverse[choice];
-#pragma unroll 1
-            for (int p = 0; p < S::PASSES; ++p) {
-              const int row = p * S::RPP + rp;
-              float acc = 0.f;
+            if constexpr (S::LPR == 32) {
+              // a row spans the warp: every lane accumulates its columns of all RT rows, one multi-row reduction
+              float acc[S::RT];
 #pragma unroll
-              for (int j = 0; j < S::QD_CPL; ++j) {
-                const int chunk = j * S::LPR + sl;
-                acc += dot32(*reinterpret_cast<const uint4*>(src + (size_t)row * (F / 2) + chunk * 16),
-                             *reinterpret_cast<const uint16_t*>(src + S::QD_CODES + (size_t)row * (F / 16) + chunk * 2), xr[j]);
+              for (int row = 0; row < S::RT; ++row) {
+                float sum = 0.f;
+#pragma unroll
+                for (int j = 0; j < S::QD_CPL; ++j) {
+                  const int chunk = j * 32 + lane;
+                  sum += dot32(*reinterpret_cast<const uint4*>(src + (size_t)row * (F / 2) + chunk * 16),
+                               *reinterpret_cast<const uint16_t*>(src + S::QD_CODES + (size_t)row * (F / 16) + chunk * 2), xr[j]);
+                }
+                acc[row] = sum;
               }
+              const float total = multi_reduce<S::RT>(acc, lane);
+              if (reduced_owner<S::RT>(lane)) {
+                const float down = round_bf16(total * scale);
+                sh.contrib[choice][local0 + reduced_row<S::RT>(lane)] = round_bf16(down * r.weight);
+              }
+            } else {
+#pragma unroll 1
+              for (int p = 0; p < S::PASSES; ++p) {
+                const int row = p * S::RPP + rp;
+                float acc = 0.f;
 #pragma unroll
-              for (int o = S::LPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-              if (sl == 0) {
-                const float down = round_bf16(acc * scale);
-                sh.contrib[choice][local0 + row] = round_bf16(down * r.weight);
+                for (int j = 0; j < S::QD_CPL; ++j) {
+                  const int chunk = j * S::LPR + sl;
+                  acc += dot32(*reinterpret_cast<const uint4*>(src + (size_t)row * (F / 2) + chunk * 16),
+                               *reinterpret_cast<const uint16_t*>(src + S::QD_CODES + (size_t)row * (F / 16) + chunk * 2), xr[j]);
+                }
+#pragma unroll
+                for (int o = S::LPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                if (sl == 0) {
+                  const float down = round_bf16(acc * scale);
+                  sh.contrib[choice][local0 + row] = round_bf16(down * r.weight);
+                }
               }
             }
             release(slot);
