@@ -263,6 +263,7 @@ struct StackShared {
   volatile long long issued;            // ring tiles the producer has issued (published after every tensor-core unit)
   int finisher;                         // this block stored the last part of the tile at hand
   float act_inverse[kSMaxTopK];         // inverse normalisers of the routed activations' digit rows
+  uint8_t seg_parts[2][8], seg_index[2][8];   // how this block's first tile segments (gate/up, down) are split: computed once
   uint8_t dn_parts[kSMaxTopK][32];      // blocks that share a down tile (route, row tile)
   unsigned dn_target[32];               // arrivals that complete a row tile: routed parts of every route + shared-expert blocks
   uint8_t sfbx[kTcDigits][256];         // E4M3 block scales of the digit rows of x
@@ -1212,18 +1213,23 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
           sact_seen |= 1u << e;
         }
         const uint4* xs = reinterpret_cast<const uint4*>(s_sact + (size_t)e * F);
-#pragma unroll 1
+        float acc[S::SD_ROWS];
+#pragma unroll
         for (int row = 0; row < S::SD_ROWS; ++row) {
-          float acc = 0.f;
+          float sum = 0.f;
 #pragma unroll 2
           for (int c = 0; c < S::SD_CPL; ++c) {
             const int chunk = c * 32 + lane;
-            acc = dot8(*reinterpret_cast<const uint4*>(src + (size_t)row * F * 2 + chunk * 16), xs[chunk], acc);
+            sum = dot8(*reinterpret_cast<const uint4*>(src + (size_t)row * F * 2 + chunk * 16), xs[chunk], sum);
           }
-          acc = warp_sum(acc);
-          if (lane == 0) {
-            if (tc) a.sd_out[((size_t)par * a.n_shared + e) * D + (size_t)plan.g0 * S::RT + local0 + row] = round_bf16(acc);
-            else sh.contrib[a.top_k + e][local0 + row] = round_bf16(acc);
+          acc[row] = sum;
+        }
+        {
+          const float total = multi_reduce<S::SD_ROWS>(acc, lane);   // one reduction for all rows of the tile
+          if (reduced_owner<S::SD_ROWS>(lane)) {
+            const int row = reduced_row<S::SD_ROWS>(lane);
+            if (tc) a.sd_out[((size_t)par * a.n_shared + e) * D + (size_t)plan.g0 * S::RT + local0 + row] = round_bf16(total);
+            else sh.contrib[a.top_k + e][local0 + row] = round_bf16(total);
           }
         }
         release(slot);
@@ -1560,6 +1566,30 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
       return sum;
     };
 
+    // the split of this block's tile segments is the same in every layer: work it out once (64-bit
+    // divisions), not in the hand-over at the end of every segment
+    if (tt < 2) {
+      const int chunks = tt == 0 ? S::GU_CHUNKS : S::DN_CHUNKS;
+      const long long total = (long long)a.top_k * (tt == 0 ? S::GU_TILES : S::DN_TILES) * chunks;
+      int u = tt == 0 ? plan.qu0 : plan.du0;
+      const int end = u + (tt == 0 ? plan.n_qu : plan.n_du);
+      for (int seg = 0; seg < 8 && u < end; ++seg) {
+        const int tg = u / chunks;
+        int index;
+        sh.seg_parts[tt][seg] = (uint8_t)tc_split((long long)tg * chunks, (long long)tg * chunks + chunks - 1, total, gridDim.x, blockIdx.x, &index);
+        sh.seg_index[tt][seg] = (uint8_t)index;
+        u = min(end, (tg + 1) * chunks);
+      }
+    }
+    tc_group_sync();
+    auto split_of = [&](int kind, int seg, int tg, int chunks, long long total, int* index) -> int {
+      if (seg < 8) {
+        *index = sh.seg_index[kind][seg];
+        return sh.seg_parts[kind][seg];
+      }
+      return tc_split((long long)tg * chunks, (long long)tg * chunks + chunks - 1, total, gridDim.x, blockIdx.x, index);
+    };
+
     for (int layer = 0; layer < a.n_layers; ++layer, base += plan.per_layer) {
       unsigned* sync = a.sync + (size_t)layer * kSyncWordsPerLayer;
       unsigned* tile_count = a.tilesync + (size_t)layer * kTileCountersPerLayer;
@@ -1577,12 +1607,11 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
         const long long total = (long long)a.top_k * S::GU_TILES * S::GU_CHUNKS;
         int u = plan.qu0;
         const int end = plan.qu0 + plan.n_qu;
-        while (u < end) {
+        for (int seg = 0; u < end; ++seg) {
           const int tg = u / S::GU_CHUNKS;
           float sum = read_segment(0);
           int index;
-          const int parts = tc_split((long long)tg * S::GU_CHUNKS, (long long)tg * S::GU_CHUNKS + S::GU_CHUNKS - 1, total,
-                                     gridDim.x, blockIdx.x, &index);
+          const int parts = split_of(0, seg, tg, S::GU_CHUNKS, total, &index);
           // A split tile is finished by the block that holds its first units: that block reaches the tile
           // last (end of its range), the others first (start of theirs), so their parts are long there.
           bool finish = true;
@@ -1673,12 +1702,12 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
         const long long total = (long long)a.top_k * S::DN_TILES * S::DN_CHUNKS;
         int u = plan.du0;
         const int end = plan.du0 + plan.n_du;
-        while (u < end) {
+        for (int seg = 0; u < end; ++seg) {
           const int tg = u / S::DN_CHUNKS;
           const int j = tg / S::DN_TILES, tile = tg % S::DN_TILES;
           const float sum = read_segment(4 * j);
           int index;
-          tc_split((long long)tg * S::DN_CHUNKS, (long long)tg * S::DN_CHUNKS + S::DN_CHUNKS - 1, total, gridDim.x, blockIdx.x, &index);
+          split_of(1, seg, tg, S::DN_CHUNKS, total, &index);
           a.dn_part[((size_t)tg * S::DN_CHUNKS + index) * kTcRows + row] = sum;
           __threadfence();
           epilogue_sync();
