@@ -548,6 +548,7 @@ __device__ __forceinline__ void stage_x_tc(unsigned char* s_xdig, uint16_t* s_xb
 __device__ __forceinline__ void tc_upload_scales(uint32_t tmem, int subpartition, const uint8_t* table, int pitch, int rows, int steps,
                                                  int lane) {
   const uint32_t base = tmem + ((uint32_t)(subpartition * 32) << 16) + kTcColSfb;
+#pragma unroll 1
   for (int s0 = 0; s0 < steps; s0 += 4) {
     uint32_t r[16];
 #pragma unroll
@@ -568,23 +569,43 @@ __device__ __forceinline__ void finish_row_tile(const StackArgs& a, StackShared*
                                                 int stride) {
   using S = StackShape<D, F>;
   (void)layer;
+  // the routes' activation maxima first (the same for every row), then per row all loads before any arithmetic:
+  // this runs in one block per row tile at the very end of a layer, so its round trips to L2 are what it costs
+  unsigned amax[kSMaxTopK];
+#pragma unroll
+  for (int j = 0; j < kSMaxTopK; ++j) amax[j] = j < a.top_k ? __ldcg(a.act_amax + par * kSMaxTopK + j) : 0u;
   for (int row = first; row < kTcRows; row += stride) {
     const size_t at_row = (size_t)tile * kTcRows + row;
+    float part[kSMaxTopK][2], shared[kSMaxShared];
+#pragma unroll
+    for (int j = 0; j < kSMaxTopK; ++j) {
+      const float* from = a.dn_part + (size_t)(j * S::DN_TILES + tile) * S::DN_CHUNKS * kTcRows + row;
+      const int parts = j < a.top_k ? sh->dn_parts[j][tile] : 0;
+      part[j][0] = parts > 0 ? __ldcg(from) : 0.f;
+      part[j][1] = parts > 1 ? __ldcg(from + kTcRows) : 0.f;
+    }
+#pragma unroll
+    for (int e = 0; e < kSMaxShared; ++e)
+      shared[e] = e < a.n_shared ? __ldcg(a.sd_out + ((size_t)par * a.n_shared + e) * D + at_row) : 0.f;
     float total = 0.f;
-    for (int j = 0; j < a.top_k; ++j) {
-      const RouteEntry& r = sh->routes[par].route[j];
-      const int parts = sh->dn_parts[j][tile];
-      const float* part = a.dn_part + (size_t)(j * S::DN_TILES + tile) * S::DN_CHUNKS * kTcRows + row;
-      float acc = 0.f;
-      for (int p = 0; p < parts; ++p) acc += __ldcg(part + (size_t)p * kTcRows);
-      if (r.dn_codes) {
-        float inverse;
-        pow2_normaliser(__ldcg(a.act_amax + par * kSMaxTopK + j), &inverse);
-        const float down = round_bf16(acc * (r.dn_scale2 * (inverse * (1.f / 512.f))));
-        total += round_bf16(down * r.weight);
+#pragma unroll
+    for (int j = 0; j < kSMaxTopK; ++j) {
+      if (j < a.top_k) {
+        const RouteEntry& r = sh->routes[par].route[j];
+        const int parts = sh->dn_parts[j][tile];
+        float acc = part[j][0] + part[j][1];   // block order; a tile cut in more than two parts is rare (narrow slices)
+        const float* from = a.dn_part + (size_t)(j * S::DN_TILES + tile) * S::DN_CHUNKS * kTcRows + row;
+        for (int p = 2; p < parts; ++p) acc += __ldcg(from + (size_t)p * kTcRows);
+        if (r.dn_codes) {
+          float inverse;
+          pow2_normaliser(amax[j], &inverse);
+          const float down = round_bf16(acc * (r.dn_scale2 * (inverse * (1.f / 512.f))));
+          total += round_bf16(down * r.weight);
+        }
       }
     }
-    for (int e = 0; e < a.n_shared; ++e) total += __ldcg(a.sd_out + ((size_t)par * a.n_shared + e) * D + at_row);
+#pragma unroll
+    for (int e = 0; e < kSMaxShared; ++e) total += shared[e];
     const size_t at = ((size_t)xpar * a.world + a.rank) * D + at_row;
     for (int r = 0; r < a.world; ++r) a.peer_inbox[r][at] = total;
   }
@@ -704,6 +725,10 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
       constexpr int kQgPerJob = 2 * F / S::QG_ROWS;
       for (int layer = 0; layer < a.n_layers && alive; ++layer) {
         const StackLayer ly = a.layers[layer];
+        if (tc) {   // the layer's four TMA descriptors live in global memory: bring them to the copy engine early
+          for (int m = 0; m < 4; ++m)
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<const unsigned char*>(ly.tmaps) + m * 128) : "memory");
+        }
         const unsigned* sync = a.sync + (size_t)layer * kSyncWordsPerLayer;
         // ---- router rows, padded to a multiple of the consumer count
         for (int t = 0; t < plan.s_sg && alive; ++t) {
@@ -1647,10 +1672,7 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
             if (lane == 0) atomicMax(a.act_amax + par * kSMaxTopK + choice, bits);
             __threadfence();
             epilogue_sync();
-            if (et == 0) {
-              __threadfence();
-              red_release_add(sync + kRtGuDone, 1u);
-            }
+            if (et == 0) red_release_add(sync + kRtGuDone, 1u);   // every writer fenced its own stores above
           }
           u = min(end, (tg + 1) * S::GU_CHUNKS);
         }
