@@ -212,6 +212,7 @@ int ink_expert_reduce(const void* down, const int64_t* indices, const void* weig
  *               conversion); with null in every layer they run on the CUDA cores.
  *  x            BF16 [hidden]: input of the first block (x, residual_io, normed_out, partial_out and every
  *               layer's norm_weight are read and written 16 bytes at a time: 16-byte aligned)
+ *  flags        bit 0 = glue, bit 1 = every layer carries bank_maps (run the routed experts on the tensor cores)
  *  glue = 0     n_layers must be 1; partial_out FP32 [hidden] receives the block's output
  *  glue = 1     residual_io BF16 [hidden] is the residual stream (updated in place),
  *               normed_out BF16 [hidden] the normalised output after the last block,
@@ -244,7 +245,7 @@ size_t ink_moe_stack_trace_offset(int n_layers, int hidden, int intermediate, in
 size_t ink_moe_stack_scratch_bytes(int n_layers, int hidden, int intermediate, int experts, int n_shared,
                                    int top_k);
 int ink_moe_stack_decode(const void* layers, int n_layers, const void* x, void* residual_io, void* normed_out,
-                         float* partial_out, int glue, float eps, int hidden, int intermediate, int experts,
+                         float* partial_out, int flags, float eps, int hidden, int intermediate, int experts,
                          int n_shared, int top_k, void* scratch, size_t scratch_bytes, int32_t* status,
                          ink_stream_t stream);
 
@@ -264,7 +265,7 @@ int ink_moe_stack_decode(const void* layers, int n_layers, const void* x, void* 
  * every other wait; no load with cluster scope touches peer memory. */
 size_t ink_moe_stack_symmetric_bytes(int n_layers, int hidden, int world);
 int ink_moe_stack_decode_tp(const void* layers, int n_layers, const void* x, void* residual_io, void* normed_out,
-                            float* partial_out, int glue, float eps, int hidden, int intermediate, int experts,
+                            float* partial_out, int flags, float eps, int hidden, int intermediate, int experts,
                             int n_shared, int top_k, void* scratch, size_t scratch_bytes, int rank, int world,
                             const uint64_t* peer_regions, int32_t* status, ink_stream_t stream);
 

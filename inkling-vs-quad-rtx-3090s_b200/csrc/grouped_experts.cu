@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(kGThreads, 1) expert_gemm_kernel(GemmArgs a) {
   __shared__ GemmShared sh;
   __shared__ int s_route[kGN];
   __shared__ float s_out_scale[kGN];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5;
   const int group = blockIdx.y, m0 = blockIdx.x * kGM;
   const int count = a.counts[group];
   if (count <= 0) return;

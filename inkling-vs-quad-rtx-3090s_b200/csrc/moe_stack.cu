@@ -729,7 +729,6 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
           for (int m = 0; m < 4; ++m)
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<const unsigned char*>(ly.tmaps) + m * 128) : "memory");
         }
-        const unsigned* sync = a.sync + (size_t)layer * kSyncWordsPerLayer;
         // ---- router rows, padded to a multiple of the consumer count
         for (int t = 0; t < plan.s_sg && alive; ++t) {
           if (!(alive = next_slot(dst, bar))) break;
