@@ -77,3 +77,16 @@ def test_encode_banks_rejects_bad_arguments():
     # shapes that do not tile by 128 rows x 256 columns
     assert lib.ink_moe_stack_encode_banks(out, 256, 1 << 20, 256, 1 << 17, 256, 1 << 20, 256, 1 << 17, 4, 1000, 512) != 0
     assert b"tile" in lib.ink_last_error()
+
+
+def test_even_spacing_of_the_banks_is_detected():
+    """The tensor-core variant needs the banks of one kind evenly spaced in memory; the host logic
+    that decides it works on addresses only."""
+    from inkling_b200.layer import ResidentExperts
+
+    spaced = ResidentExperts._even_spacing([[4096, 4096 + 1024, 4096 + 2048], [64, 64 + 256, 64 + 512]], [1024, 128])
+    assert spaced == [(4096, 1024), (64, 256)]                      # a gap between experts is fine, overlap is not
+    assert ResidentExperts._even_spacing([[4096, 4096 + 512]], [1024]) is None          # overlapping
+    assert ResidentExperts._even_spacing([[4096, 8192, 8192 + 1024]], [1024]) is None   # uneven
+    assert ResidentExperts._even_spacing([[4100, 4100 + 1024]], [1024]) is None         # misaligned
+    assert ResidentExperts._even_spacing([[4096]], [1024]) == [(4096, 1024)]            # a single expert
