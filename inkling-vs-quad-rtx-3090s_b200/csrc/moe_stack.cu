@@ -1,17 +1,23 @@
 // One persistent cooperative kernel for a whole stack of MoE blocks at decode (one
 // token): router, expert plan, routed NVFP4 and shared BF16 gate/up, down + combine and
-// the residual add + RMS norm between blocks, all inside one launch.
+// the residual add + RMS norm between blocks, all inside one launch; with several
+// tensor-parallel ranks also the all-reduce of every block (stores into the peers' inboxes).
 //
 // One block per SM. Warp 0 is the producer: it walks the block's tile list, layer after
-// layer, and keeps a 20-slot shared-memory ring full with bulk asynchronous copies; it
+// layer, and keeps a 16-slot shared-memory ring full with bulk asynchronous copies; it
 // never waits for arithmetic, only for a free slot and -- before the first routed tile
-// of a layer -- for that layer's routing. Warps 1..10 are consumers: consumer c takes
-// tiles c, c+10, ... (the ring depth is a multiple of the consumer count, see the ring
-// comment in stream_decode.cu). Warp 11 is the auxiliary warp: on the block that
-// finishes the last router row it runs the top-k / weight chain / plan for the layer.
-// Phases of a layer are ordered across blocks by three counters in global memory
-// (shared gate/up done, routed gate/up done, down done); the weight stream itself never
-// stops at them, because weight addresses do not depend on activations.
+// of a layer -- for that layer's routing. Warps 1..8 are consumers: consumer c takes
+// tiles c, c+8, ... (the ring depth is a multiple of the consumer count, see the ring
+// comment in stream_decode.cu). Warp 9 is the auxiliary warp: in every block it resolves
+// the layer's routing (top-k, weight chain, bank addresses) from the scores all blocks
+// wrote. Phases of a layer are ordered across blocks by counters in global memory (shared
+// gate/up done, routed gate/up done, rows delivered); the weight stream itself never stops
+// at them, because weight addresses do not depend on activations. Counters only grow:
+// every target is a multiple of the number of launches so far, nothing is cleared.
+//
+// Template parameter TC selects how the routed experts are computed: on the CUDA cores
+// (codes converted in registers, packed FP16 FMAs) or on the tensor cores (tc_path.cuh:
+// eight more warps, the auxiliary warp issues the MMAs).
 //
 // Every wait (ring slot, routing flag, counter) is bounded; a wait that gives up sets
 // kFlagWaitTimedOut in the status word, marks the launch as failed and every loop
