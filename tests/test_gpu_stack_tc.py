@@ -52,7 +52,8 @@ def test_full_shape_block_against_oracle(ib, device, tensor_cores):
         assert max_rel(out.float(), oracle_moe.moe_layer_fp32(x, p, cpu_banks, idx, w, gam)) <= TOL
 
 
-@pytest.mark.parametrize("shape", [(3, 1024, 512, 32), (2, 2048, 256, 32), (2, 4096, 512, 32), (2, 4096, 2048, 32)])
+@pytest.mark.parametrize("shape", [(3, 1024, 512, 32), (2, 2048, 256, 32), (2, 4096, 256, 32), (2, 4096, 512, 32),
+                                   (2, 4096, 1024, 32), (2, 4096, 2048, 32)])
 def test_stack_against_launch_by_launch_and_cuda_cores(ib, device, monkeypatch, shape):
     n_layers, d, f, experts = shape
     gen = torch.Generator().manual_seed(9)
