@@ -132,6 +132,7 @@ struct StackArgs {
   // tensor-parallel ranks (world == 1: the "peers" are this rank's own scratch)
   int rank, world;
   float* inbox;                    // this rank's [2][world][hidden] FP32: partial outputs as the ranks deliver them
+  unsigned* local_done;            // scratch [n_layers]: deliveries this rank has made (several ranks: the last one tells the peers)
   unsigned* xsync;                 // this rank's [n_layers] counters of delivered blocks
   float* peer_inbox[kSMaxWorld];   // the same two regions of every rank, as mapped into this process
   unsigned* peer_xsync[kSMaxWorld];
@@ -616,11 +617,18 @@ __device__ __forceinline__ void finish_row_tile(const StackArgs& a, StackShared*
     for (int r = 0; r < a.world; ++r) a.peer_inbox[r][at] = total;
   }
 }
-// one thread, after every row of the tile has been stored: count the tile at every rank
-__device__ __forceinline__ void deliver_row_tile(const StackArgs& a, int layer) {
+// One thread, after a piece of the layer's output (a block's rows, or a 128-row tile) has been stored
+// into every rank's inbox: count it. One rank: on the layer's counter directly. Several ranks: on a
+// counter of this rank; only the delivery that completes the rank's `pieces` tells the peers, with one
+// system-scope increment each -- hundreds of remote increments on one address per layer cost more
+// than the layer itself.
+__device__ __forceinline__ void count_delivery(const StackArgs& a, int layer, unsigned epoch1, unsigned pieces) {
   if (a.world > 1) {
     __threadfence_system();
-    for (int r = 0; r < a.world; ++r) red_release_sys_add(a.peer_xsync[r] + layer, 1u);
+    if (atomicAdd(a.local_done + layer, 1u) + 1u == epoch1 * pieces) {
+      __threadfence_system();
+      for (int r = 0; r < a.world; ++r) red_release_sys_add(a.peer_xsync[r] + layer, 1u);
+    }
   } else {
     __threadfence();
     red_release_add(a.xsync + layer, 1u);
@@ -1038,7 +1046,7 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
       const int xpar = (int)(((epoch1 - 1u) * (unsigned)a.n_layers + (unsigned)layer) & 1u);
       float* inbox = a.inbox + (size_t)xpar * a.world * D;
       // deliveries of a layer: one per block (CUDA-core variant) or per 128-row tile (tensor-core variant) and rank
-      const unsigned down_target = epoch1 * (tc ? (unsigned)S::DN_TILES : gridDim.x) * (unsigned)a.world;
+      const unsigned down_target = a.world > 1 ? epoch1 * (unsigned)a.world : epoch1 * (tc ? (unsigned)S::DN_TILES : gridDim.x);
       const float x_inverse = sh.x_inverse;
       const bool tracer = (ct == 0);
       if (tracer) INK_TRACE(layer, kTrLayerStart);
@@ -1046,12 +1054,7 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
       if (ct == 0) {
         if (plan.n_sg == 0) red_release_add(sync + kShGuDone, 1u);
         if (plan.n_q == 0 && !tc) red_release_add(sync + kRtGuDone, 1u);   // (the tensor-core path counts tiles)
-        if (!tc && plan.n_sd + plan.n_qd == 0) {
-          if (a.world > 1)
-            for (int r = 0; r < a.world; ++r) red_release_sys_add(a.peer_xsync[r] + layer, 1u);
-          else
-            red_release_add(a.xsync + layer, 1u);
-        }
+        if (!tc && plan.n_sd + plan.n_qd == 0) count_delivery(a, layer, epoch1, gridDim.x);
       }
       // ------------------------------------------------ router rows
       for (int t = first_of(plan.s_r); t < plan.s_sg; t += kSC) {
@@ -1281,7 +1284,7 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
               if (a.world > 1) __threadfence_system();
               else __threadfence();
               __syncwarp();
-              if (lane == 0) deliver_row_tile(a, layer);
+              if (lane == 0) count_delivery(a, layer, epoch1, (unsigned)S::DN_TILES);
             }
           }
         }
@@ -1389,15 +1392,7 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
             for (int r = 0; r < a.world; ++r) a.peer_inbox[r][at] = total;
           }
           __syncwarp();
-          if (lane == 0) {
-            if (a.world > 1) {
-              __threadfence_system();
-              for (int r = 0; r < a.world; ++r) red_release_sys_add(a.peer_xsync[r] + layer, 1u);
-            } else {
-              __threadfence();
-              red_release_add(a.xsync + layer, 1u);
-            }
-          }
+          if (lane == 0) count_delivery(a, layer, epoch1, gridDim.x);
         }
       }
       }   // CUDA-core routed down
@@ -1749,7 +1744,7 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
             if (a.world > 1) __threadfence_system();
             else __threadfence();
             epilogue_sync();
-            if (et == 0) deliver_row_tile(a, layer);
+            if (et == 0) count_delivery(a, layer, epoch1, (unsigned)S::DN_TILES);
           }
           u = min(end, (tg + 1) * S::DN_CHUNKS);
         }
@@ -1882,6 +1877,7 @@ extern "C" size_t ink_moe_stack_scratch_bytes(int n_layers, int hidden, int inte
   bytes += pad256(dn_part_bytes(hidden, intermediate, top_k));                  // parts of split down tiles
   bytes += pad256(sizeof(float) * 2 * (size_t)n_shared * hidden);               // shared experts' down rows
   bytes += pad256(sizeof(unsigned) * 2 * kSMaxTopK);                            // activation maxima
+  bytes += pad256(sizeof(unsigned) * (size_t)n_layers);                         // deliveries of this rank
   bytes += pad256(sizeof(unsigned) * kTileCounters * (size_t)n_layers);         // tile counters
   bytes += pad256(sizeof(float) * 2 * (size_t)(experts + n_shared));            // logits
   bytes += pad256(sizeof(float) * 2 * (size_t)experts);                         // scores
@@ -1942,6 +1938,7 @@ static int stack_decode(const void* layers, int n_layers, const void* x, void* r
   a.dn_part = (float*)take(dn_part_bytes(hidden, intermediate, top_k));
   a.sd_out = (float*)take(sizeof(float) * 2 * (size_t)n_shared * hidden);
   a.act_amax = (unsigned*)take(sizeof(unsigned) * 2 * kSMaxTopK);
+  a.local_done = (unsigned*)take(sizeof(unsigned) * (size_t)n_layers);
   a.tilesync = (unsigned*)take(sizeof(unsigned) * kTileCounters * (size_t)n_layers);
   a.logits = (float*)take(sizeof(float) * 2 * (size_t)(experts + n_shared));
   a.scores = (float*)take(sizeof(float) * 2 * (size_t)experts);
