@@ -14,9 +14,10 @@ ROOT = Path(__file__).resolve().parents[1]
 SHAPE = dict(n_layers=2, hidden=4096, intermediate=2048, experts=64, n_shared=2, top_k=6)
 
 
-def _worker(rank: int, world: int, port: int, results):
+def _worker(rank: int, world: int, port: int, results, tensor_cores: bool):
     sys.path.insert(0, str(ROOT))
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      INKLING_STACK_TENSOR_CORES="1" if tensor_cores else "0")
     import torch.distributed as dist
 
     torch.cuda.set_device(rank)
@@ -37,6 +38,7 @@ def _worker(rank: int, world: int, port: int, results):
             outs.append(stack(xs[i]).float().cpu().clone())
         torch.cuda.synchronize()
         stack._fused.check_status()
+        assert (stack._fused.bank_maps is not None) == tensor_cores
         routing = [layer.topk_indices[:1].cpu().clone() for layer in stack.layers]
         results[rank] = (torch.stack(outs), routing)
         dist.barrier()
@@ -44,7 +46,9 @@ def _worker(rank: int, world: int, port: int, results):
         dist.destroy_process_group()
 
 
-def test_two_rank_stack_matches_one_gpu():
+@pytest.mark.parametrize("tensor_cores", [False, True], ids=["cuda_cores", "tensor_cores"])
+def test_two_rank_stack_matches_one_gpu(tensor_cores, monkeypatch):
+    monkeypatch.setenv("INKLING_STACK_TENSOR_CORES", "0")   # the one-GPU stack it is compared with: the default variant
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     sys.path.insert(0, str(ROOT))
@@ -54,7 +58,7 @@ def test_two_rank_stack_matches_one_gpu():
     ctx = mp.get_context("spawn")
     results = ctx.Manager().dict()
     port = 29700 + os.getpid() % 200
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, results)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port + int(tensor_cores), results, tensor_cores)) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:
