@@ -257,6 +257,8 @@ struct StackShared {
   int done[2][3];                       // tiles finished per layer parity: shared g/u, routed g/u, down
   unsigned epoch1;                      // launches completed before this one, plus one: scales every target
   volatile int routed_layers;           // layers whose routing table is in `routes` (set by the auxiliary warp)
+  volatile int seen[3];                 // layers whose grid-wide counters (shared gate/up, routed gate/up, rows delivered) the
+                                        // auxiliary warp has seen complete: one poller per block instead of one per warp
   volatile int sact_flag[kSMaxShared];  // layers whose shared-expert activations are staged, per shared expert
   volatile int act_flag[kSMaxTopK];     // layers whose routed activations are staged, per route
   volatile int failed;
@@ -353,8 +355,10 @@ __device__ __forceinline__ bool wait_routing(int layer, StackShared* sh) {
 __device__ __forceinline__ void wait_flag(volatile int* flag, int layer, StackShared* sh, int lane) {
   if (lane == 0 && *flag <= layer) {
     const long long t0 = clock64();
-    while (*flag <= layer && !sh->failed)
+    while (*flag <= layer && !sh->failed) {
       if (clock64() - t0 > kWaitLimitCycles) sh->failed = 1;
+      __nanosleep(40);   // the warp next to this one on the scheduler is computing
+    }
   }
   __syncwarp();
   __threadfence_block();
@@ -674,6 +678,7 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
     sh.sg_done = 0;
     sh.issued = 0;
     sh.routed_layers = 0;
+    for (int i = 0; i < 3; ++i) sh.seen[i] = 0;
     for (int i = 0; i < kSMaxShared; ++i) sh.sact_flag[i] = 0;
     for (int i = 0; i < kSMaxTopK; ++i) sh.act_flag[i] = 0;
     sh.failed = 0;
@@ -899,6 +904,21 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       stack_router_tail(a, a.layers[layer], layer, &sh);
+      if (!tc && lane == 0) {
+        // One lane polls the layer's grid-wide counters for the whole block and raises a flag in shared memory
+        // for each: eight polling warps per block crowd the counter's L2 line and hold up its increments.
+        const unsigned epoch1 = sh.epoch1;
+        wait_global(sync + kShGuDone, epoch1 * gridDim.x, &sh);
+        __threadfence_block();
+        sh.seen[0] = layer + 1;
+        wait_global(sync + kRtGuDone, epoch1 * gridDim.x, &sh);
+        __threadfence_block();
+        sh.seen[1] = layer + 1;
+        if (a.world > 1) wait_system(a.xsync + layer, epoch1 * (unsigned)a.world, &sh);
+        else wait_global(a.xsync + layer, epoch1 * gridDim.x, &sh);
+        __threadfence_block();
+        sh.seen[2] = layer + 1;
+      }
       if (tc && lane == 0 && !sh.failed) {
         // ---- the routed projections on the tensor cores: one thread issues. A unit is 128 weight rows x
         // 256 columns in two ring slots; four MMAs of 64 columns each accumulate it into the tile's accumulator.
@@ -1141,7 +1161,6 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
         }
       }
       // ------------------------------------------------ routed gate/up
-      const unsigned rt_gu_target = epoch1 * gridDim.x;
       if constexpr (!tc) {
         uint32_t xr[S::QG_CPL][16];
 #pragma unroll
@@ -1197,10 +1216,12 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
       // past its gate/up tiles first.
       if (!tc && kSMaxTopK * F * 2 < D * 4) consumer_sync();
       // ------------------------------------------------ shared down
-      if (lane == 0) {
-        wait_global(sync + kShGuDone, epoch1 * gridDim.x, &sh);
-        wait_routing(layer, &sh);
+      if (tc) {
+        if (lane == 0) wait_global(sync + kShGuDone, epoch1 * gridDim.x, &sh);
+      } else {
+        wait_flag(&sh.seen[0], layer, &sh, lane);
       }
+      if (lane == 0) wait_routing(layer, &sh);
       __syncwarp();
       if (tracer) INK_TRACE(layer, kTrShGuAll);
       for (int e = cw; e < a.n_shared; e += kSC) {   // warp e stages shared expert e: act * gamma, BF16
@@ -1292,8 +1313,7 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
       if (tracer) INK_TRACE(layer, kTrShDownDone);
       if constexpr (!tc) {
       // ------------------------------------------------ routed down
-      if (lane == 0) wait_global(sync + kRtGuDone, rt_gu_target, &sh);
-      __syncwarp();
+      wait_flag(&sh.seen[1], layer, &sh, lane);
       if (tracer) INK_TRACE(layer, kTrRtGuAll);
       for (int job = cw; job < a.top_k; job += kSC) {   // warp j stages route j
         if (!sh.failed) {
@@ -1405,11 +1425,15 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
       }
       if (tracer) INK_TRACE(layer, kTrRtDownDone);
       // every block of every rank has delivered this layer's rows
-      if (lane == 0) {
-        if (a.world > 1) wait_system(a.xsync + layer, down_target, &sh);
-        else wait_global(a.xsync + layer, down_target, &sh);
+      if (tc) {
+        if (lane == 0) {
+          if (a.world > 1) wait_system(a.xsync + layer, down_target, &sh);
+          else wait_global(a.xsync + layer, down_target, &sh);
+        }
+        __syncwarp();
+      } else {
+        wait_flag(&sh.seen[2], layer, &sh, lane);
       }
-      __syncwarp();
       if (tracer) INK_TRACE(layer, kTrDownAll);
       if (!a.glue) {
         // one block only: each block writes the sum over the ranks of its own rows
