@@ -319,3 +319,124 @@ def shard_shared(gate_proj, up_proj, down_proj, rank: int, world: int):
     f = gate_proj.shape[1] // world
     sl = slice(rank * f, (rank + 1) * f)
     return gate_proj[:, sl].contiguous(), up_proj[:, sl].contiguous(), down_proj[:, :, sl].contiguous()
+
+
+# ---------------------------------------------------------------- BF16 experts
+def routed_decode_bf16_reference(x, indices, weights, banks, max_expert: int | None = None):
+    """kernels/routed_decode.cu:137-219 compiled with QUANT=0 (row_dot :85-101): BF16
+    weight banks, pointer stride 2 (kernels/grouped_experts.py:9-22 with
+    quantized=False), no scales. banks: {expert: {"gate_up_proj": BF16 [2f, d] (rows
+    interleave gate and up), "down_proj": BF16 [d, f]}}. Same roundings as the
+    NVFP4 kernels with scale 1: Y = bf16(silu(gate) * up); per route
+    bf16(bf16(dot) * w), FP32 sum in choice order. Dot products are float64 here.
+    Returns (activated BF16 [t*k, f], out FP32 [t, d])."""
+    t, d = x.shape
+    k = indices.shape[1]
+    f = next(iter(banks.values()))["gate_up_proj"].shape[0] // 2
+    if max_expert is None:
+        max_expert = max(banks)
+    activated = torch.zeros(t * k, f, dtype=BF16)
+    out = torch.zeros(t, d, dtype=torch.float32)
+    for token in range(t):
+        total = torch.zeros(d, dtype=torch.float32)
+        for choice in range(k):
+            e = int(indices[token, choice])
+            if e < 0 or e > max_expert or e not in banks:
+                continue
+            proj = (banks[e]["gate_up_proj"].double() @ x[token].double()).float()
+            gate, up = proj[0::2], proj[1::2]
+            y = (gate / (1.0 + torch.exp(-gate)) * up).to(BF16)
+            activated[token * k + choice] = y
+            down = _bf16_round((banks[e]["down_proj"].double() @ y.double()).float())
+            total += _bf16_round(down * weights[token, choice].float())
+        out[token] = total
+    return activated, out
+
+
+def routed_experts_bf16_fp32(x, indices, weights, banks):
+    """The BF16-expert layer in float64 with no intermediate rounding."""
+    out = torch.zeros(x.shape[0], x.shape[1], dtype=torch.float64)
+    for token in range(x.shape[0]):
+        for choice in range(indices.shape[1]):
+            e = int(indices[token, choice])
+            if e not in banks:
+                continue
+            proj = banks[e]["gate_up_proj"].double() @ x[token].double()
+            gate, up = proj[0::2], proj[1::2]
+            out[token] += (banks[e]["down_proj"].double() @ (gate * torch.sigmoid(gate) * up)) * weights[token, choice].double()
+    return out
+
+
+# ------------------------------------------------------------------ layer glue
+def rms_norm_reference(x, weight, eps: float):
+    """my_inkling/model.py:143-150 (the CPU branch of MyInklingRMSNorm.forward) and its
+    Triton twin kernels/decode.py:36-43: FP32 mean of squares, x * rsqrt(var + eps), the
+    normalised value rounded to the input dtype BEFORE the multiplication by the weight,
+    product in the input dtype."""
+    input_dtype = x.dtype
+    h = x.float()
+    variance = h.pow(2).mean(-1, keepdim=True)
+    h = h * torch.rsqrt(variance + eps)
+    return weight.to(input_dtype) * h.to(input_dtype)
+
+
+def add_rms_norm_reference(partial, residual, weight, eps: float):
+    """The skeleton of my_inkling/model.py:672-675 for a stack of MoE blocks: the block's
+    FP32 output is cast to BF16 (my_inkling/offloaded_experts.py:314) and added to the
+    BF16 residual stream (a BF16 tensor add), then normalised for the next block.
+    Returns (new residual BF16, normed BF16)."""
+    new_residual = residual + partial.to(residual.dtype)
+    return new_residual, rms_norm_reference(new_residual, weight, eps)
+
+
+def short_conv_reference(x, weight, history, residual=None):
+    """kernels/decode.py:65-112 (_short_conv, one new token against its cached history):
+    per channel total = sum_j history[j + 1] * w[j] (j < K - 1) + x * w[K - 1] in FP32,
+    history shifted by one with x appended (FP32), output = dtype(total + x), and with a
+    residual: dtype(fp32(output) + residual). x [bs, d]; weight [d, K] (the conv1d weight
+    [d, 1, K] squeezed); history FP32 [bs, d, K]. Returns (y, new_history)."""
+    k = weight.shape[-1]
+    current = x.float()
+    w = weight.float()
+    total = torch.zeros_like(current)
+    new_history = history.clone()
+    for j in range(k - 1):
+        previous = history[..., j + 1]
+        total = total + previous * w[:, j]
+        new_history[..., j] = previous
+    total = total + current * w[:, k - 1]
+    new_history[..., k - 1] = current
+    y = (total + current).to(x.dtype)
+    if residual is not None:
+        y = (y.float() + residual.float()).to(x.dtype)
+    return y, new_history
+
+
+def stack_reference(x, blocks, norm_weight, eps: float):
+    """A stack of MoE blocks joined the way configs with several blocks join them:
+    n_0 = x (taken as already normalised), h_0 = x; per block m = moe(n) through the
+    reference-faithful BF16 layer (moe_layer_reference), h += m, n = rms_norm(h).
+    `blocks` is a list of (p, banks). Returns dict(normed, residual, routing=[idx per
+    block], moe_out=[per block])."""
+    h, n = x.clone(), x.clone()
+    routing, outs = [], []
+    for p, banks in blocks:
+        m, idx, _, _ = moe_layer_reference(n, p, banks)
+        h = h + m
+        n = rms_norm_reference(h, norm_weight, eps)
+        routing.append(idx)
+        outs.append(m)
+    return dict(normed=n, residual=h, routing=routing, moe_out=outs)
+
+
+def stack_fp32(x, blocks, norm_weight, eps: float, routing):
+    """The same stack with the expert arithmetic of every block in float64 (no
+    intermediate rounding inside a block) for GIVEN routing -- `routing[i]` =
+    (indices, weights, gammas) of block i as the implementation under test chose them --
+    and the roundings the glue performs between blocks (BF16 block output, BF16 add,
+    RMS norm as rms_norm_reference). Returns (normed BF16, residual BF16)."""
+    h, n = x.clone(), x.clone()
+    for (p, banks), (idx, w, gam) in zip(blocks, routing):
+        m = moe_layer_fp32(n, p, banks, idx, w, gam).float()
+        h, n = add_rms_norm_reference(m, h, norm_weight, eps)
+    return n, h

@@ -89,3 +89,43 @@ def dispatch_fixture():
     indices = torch.tensor([[0, 1], [1, 2], [2, 0], [0, 2], [1, 0]])
     weights = torch.tensor([[0.2, 0.8], [0.7, 0.3], [0.4, 0.6], [0.0, 1.0], [0.6, 0.4]])
     return indices, weights
+
+
+# ------------------------------------------------------------------- glue cases
+EPS = 1e-6
+GLUE_SEED = 77
+
+
+def glue_inputs(gen):
+    """RMS norm: x BF16 [3, 256] with rows of very different scale, weight BF16 [256]."""
+    x = (torch.randn(3, 256, generator=gen) * torch.tensor([[0.05], [1.0], [30.0]])).to(BF16)
+    w = (1.0 + 0.2 * torch.randn(256, generator=gen)).to(BF16)
+    return x, w
+
+
+def sconv_inputs(gen, bs: int = 2, d: int = 256, k: int = 4):
+    """Short convolution: K consecutive tokens BF16 [bs, K, d] (the last is the decode
+    token, the others its history), taps FP32 [d, K] (the checkpoint keeps the convolutions in
+    FP32, my_inkling/model.py:743-747), decoder residual BF16 [bs, K, d]."""
+    seq = torch.randn(bs, k, d, generator=gen).to(BF16)
+    taps = torch.randn(d, k, generator=gen) * 0.3
+    residual = torch.randn(bs, k, d, generator=gen).to(BF16)
+    return seq, taps, residual
+
+
+def stack_cases() -> list[dict]:
+    """Three blocks of the 'small' shape with their own seeds (first block's x is the input)."""
+    return [dict(LAYER_CASES["small"], tokens=1, seed=40 + i, bias="randn") for i in range(3)]
+
+
+def stack_norm_weight(d: int) -> torch.Tensor:
+    gen = torch.Generator().manual_seed(GLUE_SEED + 1)
+    return (1.0 + 0.1 * torch.randn(d, generator=gen)).to(BF16)
+
+
+def bf16_banks(banks: dict) -> dict:
+    """BF16 expert banks (pointer stride 2: gate_up_proj, down_proj) with the values of the
+    NVFP4 banks: what an unquantised layer of the same experts would hold."""
+    return {e: dict(gate_up_proj=nvfp4.dequant_bf16(b["gate_up_proj"], b["gate_up_proj_scale"], b["gate_up_proj_scale2"]).contiguous(),
+                    down_proj=nvfp4.dequant_bf16(b["down_proj"], b["down_proj_scale"], b["down_proj_scale2"]).contiguous())
+            for e, b in banks.items()}

@@ -174,3 +174,83 @@ def test_tp_shards_sum_to_whole(case):
         parts = sum(moe.routed_experts_fp32(x, idx, w, {e: moe.shard_banks(b, r, world) for e, b in banks.items()})
                     for r in range(world))
         assert max_rel(parts, whole) < 1e-9
+
+
+# ------------------------------------------------------------------------ glue
+def _bf16_ulps(a, b):
+    a = a.to(BF16).view(torch.int16).to(torch.int32)
+    b = b.to(BF16).view(torch.int16).to(torch.int32)
+    a = torch.where(a < 0, -(a & 0x7FFF), a)
+    b = torch.where(b < 0, -(b & 0x7FFF), b)
+    return (a - b).abs()
+
+
+def test_rms_norm_matches_reference_module_and_triton_kernel(golden):
+    gen = torch.Generator().manual_seed(cases.GLUE_SEED)
+    x, w = cases.glue_inputs(gen)
+    got = moe.rms_norm_reference(x, w, cases.EPS)
+    assert torch.equal(got.float(), g(golden, "glue/norm_bf16"))          # the reference's own CPU arithmetic
+    got32 = moe.rms_norm_reference(x.float(), w.float(), cases.EPS)
+    assert max_rel(got32, g(golden, "glue/norm_triton_fp32")) < 1e-6
+
+
+def test_short_conv_matches_reference_module_and_triton_kernel(golden):
+    gen = torch.Generator().manual_seed(cases.GLUE_SEED)
+    cases.glue_inputs(gen)
+    seq, taps, res = cases.sconv_inputs(gen)
+    k = taps.shape[-1]
+    history = torch.zeros(seq.shape[0], seq.shape[-1], k)
+    history[..., 1:] = seq[:, : k - 1].float().transpose(1, 2)
+    y, new_history = moe.short_conv_reference(seq[:, -1], taps, history, res[:, -1])
+    # the module's convolution sums its taps in another order: a BF16 ulp on a few channels at most
+    ulps = _bf16_ulps(y, g(golden, "glue/sconv_module_bf16"))
+    assert int(ulps.max()) <= 1 and float((ulps > 0).float().mean()) < 0.02
+    y0, _ = moe.short_conv_reference(seq[:, -1], taps, history, None)
+    ulps = _bf16_ulps(y0, g(golden, "glue/sconv_module_bf16_no_residual"))
+    assert int(ulps.max()) <= 1 and float((ulps > 0).float().mean()) < 0.02
+    # FP32 run of the Triton kernel: same taps, same order, same history update
+    y32, h32 = moe.short_conv_reference(seq[:, -1].float(), taps, history, res[:, -1].float())
+    assert max_rel(y32, g(golden, "glue/sconv_triton_fp32")) < 1e-6
+    assert torch.equal(h32, g(golden, "glue/sconv_triton_history"))
+    assert torch.equal(new_history, h32)
+
+
+def test_stack_of_blocks_matches_reference_modules(golden):
+    blocks = [cases.make_layer(**c) for c in cases.stack_cases()]
+    x = blocks[0][2][:1]
+    weight = cases.stack_norm_weight(x.shape[-1])
+    got = moe.stack_reference(x, [(p, banks) for p, banks, _ in blocks], weight, cases.EPS)
+    for i in range(len(blocks)):
+        want_idx = g(golden, f"stack/{i}/indices")
+        assert torch.equal(got["routing"][i][0].sort().values, want_idx.sort().values), i
+        assert max_rel(got["moe_out"][i].float(), g(golden, f"stack/{i}/moe_out")) < 1e-2
+    assert max_rel(got["residual"].float(), g(golden, f"stack/{len(blocks) - 1}/residual")) < 1e-2
+    assert max_rel(got["normed"].float(), g(golden, f"stack/{len(blocks) - 1}/normed")) < 1e-2
+    # and the float64 yard-stick driven by the reference's routing stays within the bar of it
+    routing = []
+    n = x.clone()
+    h = x.clone()
+    for i, (p, banks, _) in enumerate(blocks):
+        _, w, idx, gam = moe.router(n, p["router_weight"], p["router_bias"], p["global_scale"], p["route_scale"],
+                                    p["top_k"], p["n_shared"])
+        routing.append((idx, w, gam))
+        m = moe.moe_layer_fp32(n, p, banks, idx, w, gam).float()
+        h, n = moe.add_rms_norm_reference(m, h, weight, cases.EPS)
+    fp_n, fp_h = moe.stack_fp32(x, [(p, banks) for p, banks, _ in blocks], weight, cases.EPS, routing)
+    assert max_rel(fp_n.float(), g(golden, f"stack/{len(blocks) - 1}/normed")) < 2e-2
+    assert max_rel(fp_h.float(), g(golden, f"stack/{len(blocks) - 1}/residual")) < 2e-2
+
+
+@pytest.mark.parametrize("name", ["tiny", "small"])
+def test_bf16_bank_gemv_matches_reference_cuda_file(golden, name):
+    c = cases.LAYER_CASES[name]
+    p, banks, x = cases.make_layer(**c)
+    bf = cases.bf16_banks(banks)
+    idx = g(golden, f"{name}/router_indices")
+    w = g(golden, f"{name}/router_weights", BF16)
+    act, out = moe.routed_decode_bf16_reference(x, idx, w, bf)
+    want_act, want_out = g(golden, f"{name}/bf16_gemv_activated"), g(golden, f"{name}/bf16_gemv_out")
+    assert not torch.isnan(want_out).any()
+    assert max_rel(act.float(), want_act) < 8e-3
+    assert max_rel(out, want_out) < 8e-3
+    assert max_rel(want_out, moe.routed_experts_bf16_fp32(x, idx, w, bf)) < 2e-2
