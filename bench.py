@@ -7,10 +7,16 @@
 
 A step is one decode token through `--layers` (default 40) MoE blocks of the Inkling-Small
 shape (hidden 4096; 256 NVFP4 experts of width 2048, top-6; 2 shared BF16 experts; router
-258 x 4096) under CUDA-graph replay, experts sharded tensor-parallel on the FFN width with
-one NCCL all-reduce per block. Weights are seeded synthetic N(0, 0.02) quantised to NVFP4
-(no checkpoint offline); every step gets a fresh N(0, 1) activation vector, and the 7.5 GB
-of weights a step streams are far larger than the 126 MB L2. Prints ONE JSON line.
+258 x 4096) under CUDA-graph replay, experts sharded tensor-parallel on the FFN width. The
+whole stack is ONE persistent kernel launch per token and rank; with several ranks the
+all-reduce of every block happens inside that kernel (each rank stores its FP32 partial rows
+as tagged 8-byte words into the other ranks' memory over NVLink and sums what it receives
+in rank order): no NCCL call is in the timed region. Weights are seeded synthetic N(0, 0.02)
+quantised to NVFP4 (no checkpoint offline); every step gets a fresh N(0, 1) activation
+vector, and the 7.5 GB of weights a step streams are far larger than the 126 MB L2. Outside
+the timed region the run checks itself (`parity` in the JSON line): every rank ends with the
+same bits, a two-block stack sliced across the ranks agrees with the same two blocks on one
+GPU, and no wait inside the kernel timed out. Prints ONE JSON line.
 """
 from __future__ import annotations
 
@@ -175,7 +181,8 @@ def config_dict(args, world: int) -> dict:
         "workload": f"configs[2]: stack of {args.layers} MoE blocks, 1 decode token per step, CUDA-graph replay",
         "layers": args.layers, "hidden": HIDDEN, "moe_intermediate": INTERMEDIATE, "routed_experts": EXPERTS,
         "shared_experts": N_SHARED, "top_k": TOP_K, "tokens_per_step": 1,
-        "parallelism": f"tp{world} on the FFN width, 1 all-reduce per block" if world > 1 else "tp1",
+        "parallelism": (f"tp{world} on the FFN width, 1 all-reduce per block done inside the one-launch kernel "
+                        "(tagged peer stores over NVLink, no NCCL call per token)") if world > 1 else "tp1",
         "l2": "inputs larger than L2: each step streams 7.5 GB of weights, fresh activations per step",
     }
 
@@ -268,6 +275,8 @@ def run_ours(args) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
     finite = bool(torch.isfinite(host_out.float()).all())
+    stack._fused.check_status()   # raises if any wait inside the kernel gave up (a collective with several ranks)
+    parity = self_check(ib, stack, runner, dev_x[args.warmup], device, group, rank, world)
 
     # ---- per-kernel durations for the roofline: the same kernel launched once per block of
     # the stack (distinct weights each time, so nothing is L2-warm), captured into a CUDA
@@ -352,7 +361,7 @@ def run_ours(args) -> None:
             "router_plan_launch_ms": kernel_ms["router_plan"], "add_rmsnorm_launch_ms": kernel_ms["add_rmsnorm"],
             "layer_bytes_per_rank": bytes_["total"],
         },
-        "build_seconds": build_s, "layers_built": layers, "output_finite": finite,
+        "build_seconds": build_s, "layers_built": layers, "output_finite": finite, "parity": parity,
     }
     if layers != args.layers:
         line["config"]["workload"] += f" (only {layers} blocks fit in free device memory)"
@@ -366,6 +375,59 @@ def run_ours(args) -> None:
                       f"scaled to {layers} blocks per token", "block_seconds": seconds}
     print(json.dumps(line), flush=True)
     leave(world)
+
+
+def self_check(ib, stack, runner, x, device, group, rank: int, world: int) -> dict:
+    """Outside the timed region: (1) the output of the last replay is bit-identical on every rank
+    (the replicated routers of the next block need that); (2) a two-block stack of the full shapes
+    sliced across the ranks against the same two blocks unsliced on rank 0 -- with one rank: the
+    one-launch kernel against the launch-by-launch kernels on the first two blocks of the stack --
+    as max|a-b|/max|b| (bar 2e-2) and per element with a floor of 5 % of the largest magnitude."""
+    import torch
+    import torch.distributed as dist
+
+    def errors(a, b):
+        a, b = a.double().cpu(), b.double().cpu()
+        floor = 0.05 * b.abs().max().clamp_min(1e-30)
+        return float((a - b).abs().max() / b.abs().max().clamp_min(1e-30)), float(((a - b).abs() / b.abs().clamp_min(floor)).max())
+
+    runner.token_in.copy_(x)
+    out = runner.replay()
+    bits = out.view(torch.int16).to(torch.int64)
+    checksum = (bits * torch.arange(1, bits.numel() + 1, device=device).view_as(bits)).sum().view(1)
+    identical = True
+    if world > 1:
+        sums = [torch.zeros_like(checksum) for _ in range(world)]
+        dist.all_gather(sums, checksum, group=group)
+        identical = all(int(t.item()) == int(sums[0].item()) for t in sums)
+        sliced = ib.MoEStack.synthetic(2, HIDDEN, INTERMEDIATE, EXPERTS, N_SHARED, TOP_K, device, seed=7000,
+                                       device_mesh=group, rank=rank, world=world, bias_std=0.05)
+        got = sliced(x).float().clone()
+        torch.cuda.synchronize()
+        sliced._fused.check_status()
+        result = {"ranks_identical": identical, "checked": f"2 blocks sliced over {world} ranks vs the same blocks on one GPU"}
+        if rank == 0:
+            whole = ib.MoEStack.synthetic(2, HIDDEN, INTERMEDIATE, EXPERTS, N_SHARED, TOP_K, device, seed=7000,
+                                          bias_std=0.05)
+            want = whole(x).float().clone()
+            torch.cuda.synchronize()
+            same_routing = all(torch.equal(a.topk_indices[:1].sort(-1).values, b.topk_indices[:1].sort(-1).values)
+                               for a, b in zip(sliced.layers, whole.layers))
+            result["max_rel"], result["max_rel_floor"] = errors(got, want)
+            result["same_routing"] = same_routing
+            result["ok"] = bool(identical and result["max_rel"] <= 2e-2)
+        dist.barrier(group)
+        return result
+    first_two = ib.MoEStack(list(stack.layers[:2]), HIDDEN)
+    fused = first_two(x).float().clone()
+    torch.cuda.synchronize()
+    first_two._fused.check_status()
+    first_two.one_launch = False
+    plain = first_two(x).float().clone()
+    torch.cuda.synchronize()
+    max_rel, max_rel_floor = errors(fused, plain)
+    return {"ranks_identical": True, "checked": "first 2 blocks: one-launch kernel vs launch-by-launch kernels",
+            "max_rel": max_rel, "max_rel_floor": max_rel_floor, "ok": bool(max_rel <= 2e-2)}
 
 
 def run_batched(args) -> None:

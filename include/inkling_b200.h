@@ -73,7 +73,9 @@ int ink_router_forward(const void* x, const void* weight, const float* bias, con
  * first call outside stream capture. All calls share the one array and the kernel reads
  * what the previous call left there only after re-zeroing the counter, so calls must not
  * overlap on the GPU (issue them on one stream, or order them yourself): two calls in
- * flight at once race on the scratch. */
+ * flight at once race on the scratch. The address is looked up for the device that is
+ * current at the call, so `stream` must belong to that device; and it is kept for the life
+ * of the process, so the process must not reset the device (cudaDeviceReset) in between. */
 int ink_router_forward_static(const void* x, const void* weight, const float* bias, const void* global_scale,
                               float route_scale, int tokens, int hidden, int n_routed, int n_shared, int top_k,
                               void* routed_logits, void* topk_weights, int64_t* topk_indices,
@@ -107,8 +109,11 @@ int ink_expert_plan(const int64_t* indices, const int64_t* sources, int64_t* poi
  * gate_up / down_reduce (kernels/routed_decode.cu:137-173, :178-219):
  *   activated[route] = bf16(silu(gate) * up)        gate/up = scale2 * (W_gate_up . x)
  *   output[token]    = sum over choices of fp32(bf16(bf16(scale2 * (W_down . activated[route])) * w))
- * NVFP4 banks (quantized = 1) only in this build. output is fully overwritten;
- * activated is scratch [tokens*top_k, intermediate].
+ * quantized = 1: NVFP4 banks as above. quantized = 0: the unquantised expert layer (the
+ * reference's QUANT=0 build, kernels/routed_decode.cu:85-101): pointer table [expert][2] =
+ * (gate_up_proj BF16 [2f, hidden], down_proj BF16 [hidden, f]), bank order of
+ * expert_bank_names(False) (kernels/grouped_experts.py:9-22), same roundings with scale2 = 1.
+ * output is fully overwritten; activated is scratch [tokens*top_k, intermediate].
  *  status: optional int32 device word; bit 0 is set when a route names an expert
  *          outside [0, max_expert] (the reference skips such routes silently).
  * Constraints: hidden and intermediate powers of two between 64 and 4096; top_k <= 30;
@@ -164,6 +169,21 @@ int ink_moe_down(const void* x, const int64_t* indices, const void* weights, con
 int ink_add_rmsnorm(const float* partial, void* residual, const void* weight, float eps, void* normed,
                     int tokens, int hidden, ink_stream_t stream);
 
+/* The decode step of MyInklingShortConv (my_inkling/model.py:400-409), i.e. the Triton kernel
+ * _short_conv (kernels/decode.py:65-146), which follows the MoE block as mlp_sconv with the
+ * decoder residual (my_inkling/model.py:674-675): per channel c
+ *   total = sum_{j < K-1} history[c][j+1] * taps[c][j] + x[c] * taps[c][K-1]      (FP32, tap order)
+ *   history[c] <- (history[c][1..K-1], x[c])                                       (shifted in place)
+ *   y[c] = bf16(total + x[c]);  with a residual: y[c] = bf16(fp32(y[c]) + residual[c])
+ *  x         BF16 [batch, hidden], or with x_is_fp32 = 1 the block's all-reduced FP32 output
+ *            [batch, hidden], which is rounded to BF16 first (my_inkling/offloaded_experts.py:314)
+ *  taps      FP32 [hidden, kernel_size] (conv1d.weight [hidden, 1, K]; the checkpoint keeps it FP32)
+ *  history   FP32 [batch, hidden, kernel_size], updated in place
+ *  residual  BF16 [batch, hidden] or NULL;  y BF16 [batch, hidden]
+ * kernel_size 2..4 (the model uses 4). */
+int ink_short_conv(const void* x, int x_is_fp32, const float* taps, float* history, const void* residual,
+                   void* y, int batch, int hidden, int kernel_size, ink_stream_t stream);
+
 /* ------------------------------------------------------ grouped projections ------
  * Replace the Triton kernels expert_gemm (kernels/grouped_experts.py:26-148) and
  * expert_reduce (:152-186) for more than a handful of tokens, on the tcgen05 tensor cores.
@@ -218,9 +238,13 @@ int ink_expert_reduce(const void* down, const int64_t* indices, const void* weig
  *               normed_out BF16 [hidden] the normalised output after the last block,
  *               partial_out the last block's FP32 output
  *  scratch      ink_moe_stack_scratch_bytes(...) bytes, ZERO-FILLED once before the first call and then
- *               left alone: its counters only grow (each launch reads how many launches came before).
- *               After a launch that reported a timed-out wait, zero it again before reuse.
- *  status       optional int32 word: bit 1 is set if a bounded wait inside the kernel gave up
+ *               left alone: its counters only grow (each launch reads how many launches came before;
+ *               comparisons are modulo 2^32, so the count may wrap) and its hand-over words carry the
+ *               tag of the launch and layer that wrote them. After a launch that reported a timed-out
+ *               wait, zero it again before reuse.
+ *  status       optional int32 word: bit 1 is set if a bounded wait inside the kernel gave up (the
+ *               output of that launch is invalid; later launches on the same scratch give up too until
+ *               it is zeroed again)
  * Built shapes (hidden, intermediate): (4096, 2048|1024|512|256), (2048, 256), (1024, 512);
  * experts <= 512, top_k <= 8, n_shared <= 2. The device must support cooperative launches.
  */
@@ -253,21 +277,30 @@ int ink_moe_stack_decode(const void* layers, int n_layers, const void* x, void* 
  * width, inputs and router replicated), with the all-reduce of every block done INSIDE the
  * kernel: it stands in for the per-block all-reduce of my_inkling/offloaded_experts.py:310 and
  * my_inkling/tp_plan.py:146 (kernels/paired_all_reduce.py:146-160). After the down projection
- * every block stores its rows of the FP32 partial into a region of every rank (plain stores over
- * NVLink into peer memory, then a system-scope release increment of that rank's counter); each
- * rank sums the `world` deliveries in rank order, so all ranks get the same bits. Every rank
- * launches this with the same arguments but its own layers/scratch and rank number.
+ * the block that owns a group of output rows stores its FP32 partial of them into slot `rank` of
+ * every rank's region as 8-byte words {value, tag of this launch and layer} (plain stores over
+ * NVLink into peer memory: no fence, no counter); the same block then polls its own region for
+ * those rows from every rank, adds them in rank order -- so all ranks get the same bits -- and
+ * publishes the sums to the blocks of its own GPU the same way. Every rank launches this with the
+ * same arguments but its own layers/scratch and rank number.
  *  peer_regions  host array of `world` addresses: region r is rank r's buffer of
  *                ink_moe_stack_symmetric_bytes(n_layers, hidden, world) bytes as mapped into THIS
  *                process (peer access enabled; e.g. torch symmetric memory). Zero-filled once on
  *                every rank before any rank's first launch, then left alone like the scratch.
- * All ranks must issue the same sequence of launches. Waits on other ranks are bounded like
- * every other wait; no load with cluster scope touches peer memory. */
+ * All ranks must issue the same sequence of launches (the tags are derived from the launch count),
+ * and after a launch that timed out every rank zeroes scratch and region before any rank launches
+ * again. Waits on other ranks are bounded like every other wait; no load with cluster scope
+ * touches peer memory. */
 size_t ink_moe_stack_symmetric_bytes(int n_layers, int hidden, int world);
 int ink_moe_stack_decode_tp(const void* layers, int n_layers, const void* x, void* residual_io, void* normed_out,
                             float* partial_out, int flags, float eps, int hidden, int intermediate, int experts,
                             int n_shared, int top_k, void* scratch, size_t scratch_bytes, int rank, int world,
                             const uint64_t* peer_regions, int32_t* status, ink_stream_t stream);
+/* How many SM clocks a wait inside the one-launch kernel may take before the launch gives up and
+ * reports bit 1 of `status` (default 200 000 000, about a tenth of a second; at least 1000). Applies
+ * to launches issued after the call, process-wide. Stands in for nothing in the reference, whose
+ * kernels never wait on one another; it exists so that the give-up path can be exercised quickly. */
+int ink_moe_stack_set_wait_limit(long long cycles);
 
 #ifdef __cplusplus
 }

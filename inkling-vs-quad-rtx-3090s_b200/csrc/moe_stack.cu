@@ -10,10 +10,14 @@
 // tiles c, c+8, ... (the ring depth is a multiple of the consumer count, see the ring
 // comment in stream_decode.cu). Warp 9 is the auxiliary warp: in every block it resolves
 // the layer's routing (top-k, weight chain, bank addresses) from the scores all blocks
-// wrote. Phases of a layer are ordered across blocks by counters in global memory (shared
-// gate/up done, routed gate/up done, rows delivered); the weight stream itself never stops
-// at them, because weight addresses do not depend on activations. Counters only grow:
-// every target is a multiple of the number of launches so far, nothing is cleared.
+// wrote. The gate/up phases of a layer are ordered across blocks by counters in global memory
+// (shared gate/up done, routed gate/up done); the weight stream itself never stops at them,
+// because weight addresses do not depend on activations. Counters only grow: every target is a
+// multiple of the number of launches so far, nothing is cleared, comparisons are modulo 2^32.
+// What one block hands to all others in small pieces -- router scores, output rows -- travels
+// as 8-byte words {FP32 value, tag of this launch and layer}: the reader polls the word it is
+// about to use, so there is no fence, no counter and no last-arrival serialisation on that
+// path, within a GPU and across GPUs alike (an aligned 8-byte store is one transaction).
 //
 // Template parameter TC selects how the routed experts are computed: on the CUDA cores
 // (codes converted in registers, packed FP16 FMAs) or on the tensor cores (tc_path.cuh:
@@ -69,7 +73,7 @@ __device__ __forceinline__ unsigned long long global_ns() {
       a.trace[((size_t)(layer) * kTraceBlocks + blockIdx.x) * kTraceSlots + (slot)] = global_ns();      \
   } while (0)
 
-enum SyncWord { kShGuDone = 0, kRtGuDone = 1, kRouterRows = 3, kRouteReady = 4 };
+enum SyncWord { kShGuDone = 0, kRtGuDone = 1 };
 
 // What the layer's routing resolved to: written once per layer by the auxiliary warp
 // of one block, read by every producer and consumer.
@@ -117,8 +121,8 @@ struct StackArgs {
   uint16_t* residual;              // [2][hidden] BF16: slot 0 holds the incoming residual stream (glue mode)
   uint16_t* normed_out;            // [hidden] BF16 output of the last norm (glue mode)
   float* partial;                  // [hidden] FP32 output of the (last) block
-  float* logits;                   // scratch [2][experts + n_shared]
-  float* scores;                   // scratch [2][experts]
+  unsigned long long* logits;      // scratch [2][experts + n_shared] tagged words {BF16-rounded logit, tag}
+  unsigned long long* scores;      // scratch [2][experts] tagged words {selection score, tag}
   uint16_t* activated;             // scratch [2][top_k][f]
   uint16_t* shared_activated;      // scratch [2][n_shared][f]
   RouteTable* routes;              // scratch [n_layers]
@@ -129,13 +133,12 @@ struct StackArgs {
   unsigned* tilesync;              // scratch [n_layers][tile counters]: blocks that have stored their part of a tile (epoch-based)
   unsigned* sync;                  // scratch [n_layers][kSyncWordsPerLayer]: counters that only grow (see epoch)
   unsigned* epoch;                 // scratch: launches completed so far on this rank; every target scales with it
-  // tensor-parallel ranks (world == 1: the "peers" are this rank's own scratch)
+  // tensor-parallel ranks
   int rank, world;
-  float* inbox;                    // this rank's [2][world][hidden] FP32: partial outputs as the ranks deliver them
-  unsigned* local_done;            // scratch [n_layers]: deliveries this rank has made (several ranks: the last one tells the peers)
-  unsigned* xsync;                 // this rank's [n_layers] counters of delivered blocks
-  float* peer_inbox[kSMaxWorld];   // the same two regions of every rank, as mapped into this process
-  unsigned* peer_xsync[kSMaxWorld];
+  unsigned long long* inbox;       // this rank's [2][world][hidden] tagged words: partial output rows as the ranks deliver them
+  unsigned long long* peer_inbox[kSMaxWorld];   // the same region of every rank, as mapped into this process
+  unsigned long long* summed;      // scratch [2][hidden] tagged words: the rows summed over the ranks, for every block of this rank
+  long long wait_limit;            // SM clocks a wait may take before the launch gives up
   int32_t* status;
   unsigned long long* trace;       // optional [n_layers][kTraceBlocks][kTraceSlots] nanosecond stamps
 };
@@ -256,9 +259,10 @@ struct StackShared {
   float x_inverse;                      // inverse normaliser of the staged x
   int done[2][3];                       // tiles finished per layer parity: shared g/u, routed g/u, down
   unsigned epoch1;                      // launches completed before this one, plus one: scales every target
+  long long limit;                      // SM clocks a wait may take
   volatile int routed_layers;           // layers whose routing table is in `routes` (set by the auxiliary warp)
-  volatile int seen[3];                 // layers whose grid-wide counters (shared gate/up, routed gate/up, rows delivered) the
-                                        // auxiliary warp has seen complete: one poller per block instead of one per warp
+  volatile int seen[2];                 // layers whose grid-wide counters (shared gate/up, routed gate/up) the auxiliary
+                                        // warp has seen complete: one poller per block instead of one per warp
   volatile int sact_flag[kSMaxShared];  // layers whose shared-expert activations are staged, per shared expert
   volatile int act_flag[kSMaxTopK];     // layers whose routed activations are staged, per route
   volatile int failed;
@@ -301,13 +305,16 @@ __device__ __forceinline__ void red_release_sys_add(unsigned* p, unsigned v) {
 }
 
 // Bounded wait for a global counter to reach `target`. One lane polls.
+// (Counters and targets wrap at 2^32 after some tens of millions of launches: the comparison is on the
+// signed difference, which stays right as long as a counter is less than 2^31 away from its target.)
+__device__ __forceinline__ bool reached(unsigned counter, unsigned target) { return (int)(counter - target) >= 0; }
 __device__ __forceinline__ bool wait_global(const unsigned* p, unsigned target, StackShared* sh) {
   if (sh->failed) return false;
-  if (ld_acquire_u32(p) >= target) return true;
+  if (reached(ld_acquire_u32(p), target)) return true;
   const long long t0 = clock64();
-  while (ld_acquire_u32(p) < target) {
+  while (!reached(ld_acquire_u32(p), target)) {
     if (sh->failed) return false;
-    if (clock64() - t0 > kWaitLimitCycles) {
+    if (clock64() - t0 > sh->limit) {
       sh->failed = 1;
       return false;
     }
@@ -316,20 +323,47 @@ __device__ __forceinline__ bool wait_global(const unsigned* p, unsigned target, 
   return true;
 }
 
-// The same for a counter that other GPUs add to.
-__device__ __forceinline__ bool wait_system(const unsigned* p, unsigned target, StackShared* sh) {
-  if (sh->failed) return false;
-  if (ld_acquire_sys_u32(p) >= target) return true;
+// ---- tagged words: {FP32 value (low half), tag (high half)} in one aligned 8-byte word
+__device__ __forceinline__ unsigned long long tagged(float v, unsigned tag) {
+  return (unsigned long long)__float_as_uint(v) | ((unsigned long long)tag << 32);
+}
+__device__ __forceinline__ void st_tagged(unsigned long long* p, float v, unsigned tag) {
+  asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(p), "l"(tagged(v, tag)) : "memory");
+}
+__device__ __forceinline__ void st_tagged_sys(unsigned long long* p, float v, unsigned tag) {   // into a peer's memory
+  asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p), "l"(tagged(v, tag)) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_tagged(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long ld_tagged_sys(const unsigned long long* p) {   // written by a peer
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void ld_tagged2(const unsigned long long* p, unsigned long long (&v)[2]) {   // 16-byte aligned pair
+  asm volatile("ld.relaxed.gpu.global.v2.b64 {%0, %1}, [%2];" : "=l"(v[0]), "=l"(v[1]) : "l"(p) : "memory");
+}
+__device__ __forceinline__ bool has_tag(unsigned long long word, unsigned tag) { return (unsigned)(word >> 32) == tag; }
+__device__ __forceinline__ float value_of(unsigned long long word) { return __uint_as_float((unsigned)word); }
+// The tag of a layer of a launch. Never zero before the epoch wraps, so a zero-filled buffer matches nothing.
+__device__ __forceinline__ unsigned layer_tag(unsigned epoch1, int n_layers, int layer) {
+  return epoch1 * (unsigned)n_layers + (unsigned)layer;
+}
+// Bounded wait for one tagged word; the value, or 0 once the launch has failed.
+__device__ __forceinline__ float wait_tagged(const unsigned long long* p, unsigned tag, StackShared* sh) {
+  unsigned long long w = ld_tagged(p);
+  if (has_tag(w, tag)) return value_of(w);
   const long long t0 = clock64();
-  while (ld_acquire_u32(p) < target || ld_acquire_sys_u32(p) < target) {   // cheap poll first, system-scope acquire to finish
-    if (sh->failed) return false;
-    if (clock64() - t0 > kWaitLimitCycles) {
-      sh->failed = 1;
-      return false;
-    }
+  while (!sh->failed) {
+    w = ld_tagged(p);
+    if (has_tag(w, tag)) return value_of(w);
+    if (clock64() - t0 > sh->limit) sh->failed = 1;
     __nanosleep(32);
   }
-  return true;
+  return 0.f;
 }
 
 // Bounded wait until this block's auxiliary warp has resolved the routing of `layer`.
@@ -342,7 +376,7 @@ __device__ __forceinline__ bool wait_routing(int layer, StackShared* sh) {
   const long long t0 = clock64();
   while (sh->routed_layers <= layer) {
     if (sh->failed) return false;
-    if (clock64() - t0 > kWaitLimitCycles) {
+    if (clock64() - t0 > sh->limit) {
       sh->failed = 1;
       return false;
     }
@@ -356,7 +390,7 @@ __device__ __forceinline__ void wait_flag(volatile int* flag, int layer, StackSh
   if (lane == 0 && *flag <= layer) {
     const long long t0 = clock64();
     while (*flag <= layer && !sh->failed) {
-      if (clock64() - t0 > kWaitLimitCycles) sh->failed = 1;
+      if (clock64() - t0 > sh->limit) sh->failed = 1;
       __nanosleep(40);   // the warp next to this one on the scheduler is computing
     }
   }
@@ -369,14 +403,46 @@ __device__ __forceinline__ void consumer_sync() {
 }
 
 // -------------------------------------------------------------------- router tail
-// One warp. logits/scores of the layer are complete in global memory.
-__device__ void stack_router_tail(const StackArgs& a, const StackLayer& ly, int layer, StackShared* sh) {
+// One warp. Waits for the layer's scores as the blocks publish them (tagged words), then
+// resolves the routing. Returns false if the launch failed while waiting.
+__device__ bool stack_router_tail(const StackArgs& a, const StackLayer& ly, int layer, StackShared* sh) {
   const int lane = threadIdx.x & 31;
   const int par = layer & 1;
-  const float* logit = a.logits + (size_t)par * (a.experts + a.n_shared);
-  const float* scores = a.scores + (size_t)par * a.experts;
+  const unsigned tag = layer_tag(sh->epoch1, a.n_layers, layer);
+  const unsigned long long* logit = a.logits + (size_t)par * (a.experts + a.n_shared);
+  const unsigned long long* scores = a.scores + (size_t)par * a.experts;
   float* score = sh->score;
-  for (int e = lane; e < a.experts; e += 32) score[e] = __ldcg(scores + e);
+  {
+    // all of the lane's words in one round trip, then only the missing ones again
+    constexpr int kPerLane = kSMaxExperts / 32;
+    unsigned missing = 0;
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+      const int e = i * 32 + lane;
+      if (e < a.experts) {
+        const unsigned long long w = ld_tagged(scores + e);
+        if (has_tag(w, tag)) score[e] = value_of(w);
+        else missing |= 1u << i;
+      }
+    }
+    const long long t0 = clock64();
+    while (__any_sync(0xffffffffu, missing != 0) && !sh->failed) {
+      __nanosleep(64);
+#pragma unroll
+      for (int i = 0; i < kPerLane; ++i) {
+        if ((missing >> i) & 1u) {
+          const int e = i * 32 + lane;
+          const unsigned long long w = ld_tagged(scores + e);
+          if (has_tag(w, tag)) {
+            score[e] = value_of(w);
+            missing &= ~(1u << i);
+          }
+        }
+      }
+      if (clock64() - t0 > sh->limit) sh->failed = 1;
+    }
+    if (sh->failed) return false;
+  }
   __syncwarp();
   int my_choice = 0;
 #pragma unroll 1
@@ -408,8 +474,8 @@ __device__ void stack_router_tail(const StackArgs& a, const StackLayer& ly, int 
   const int n = a.top_k + a.n_shared;
   const bool live = lane < n;
   float l = 0.f;
-  if (lane < a.top_k) l = __ldcg(logit + my_choice);
-  else if (live) l = __ldcg(logit + a.experts + (lane - a.top_k));
+  if (lane < a.top_k) l = wait_tagged(logit + my_choice, tag, sh);
+  else if (live) l = wait_tagged(logit + a.experts + (lane - a.top_k), tag, sh);
   const float lp = live ? round_bf16(fminf(0.f, l) - log1pf(__expf(-fabsf(l)))) : -INFINITY;
   float m = lp;
 #pragma unroll
@@ -448,6 +514,7 @@ __device__ void stack_router_tail(const StackArgs& a, const StackLayer& ly, int 
     __threadfence_block();
     sh->routed_layers = layer + 1;   // the producer and the consumers of this block may read the table
   }
+  return true;
 }
 
 // ---------------------------------------------------------------- x staging (consumers)
@@ -488,7 +555,7 @@ __device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity, StackSha
   const long long t0 = clock64();
   while (!mbar_try_wait(bar, parity)) {
     if (sh->failed) return false;
-    if (clock64() - t0 > kWaitLimitCycles) {
+    if (clock64() - t0 > sh->limit) {
       sh->failed = 1;
       return false;
     }
@@ -507,7 +574,7 @@ __device__ __forceinline__ bool tc_wait_issued(long long tile, StackShared* sh) 
   const long long t0 = clock64();
   while (sh->issued <= tile) {
     if (sh->failed) return false;
-    if (clock64() - t0 > kWaitLimitCycles) {
+    if (clock64() - t0 > sh->limit) {
       sh->failed = 1;
       return false;
     }
@@ -571,6 +638,50 @@ __device__ __forceinline__ void tc_upload_scales(uint32_t tmem, int subpartition
   tc_fence_before();
 }
 
+// ---- hand-over of the layer's output rows (the all-reduce of a block, for any number of ranks)
+// The thread that holds this rank's total of output row `row` stores it, tagged, where the rows are
+// summed: one rank -> straight into `summed`; several ranks -> into slot `rank` of every rank's inbox
+// (plain 8-byte stores into peer memory).
+template <int D>
+__device__ __forceinline__ void send_row(const StackArgs& a, int xpar, unsigned tag, int row, float total) {
+  if (a.world == 1) {
+    st_tagged(a.summed + (size_t)xpar * D + row, total, tag);
+  } else {
+    const size_t at = ((size_t)xpar * a.world + a.rank) * D + row;
+    for (int r = 0; r < a.world; ++r) st_tagged_sys(a.peer_inbox[r] + at, total, tag);
+  }
+}
+// Several ranks: the same thread then waits for that row from every rank (all loads of a round in
+// flight together, bounded), adds them in rank order -- every rank computes the same bits -- and
+// publishes the sum for the blocks of this rank.
+template <int D>
+__device__ __forceinline__ void gather_row(const StackArgs& a, StackShared* sh, int xpar, unsigned tag, int row) {
+  const unsigned long long* from = a.inbox + (size_t)xpar * a.world * D + row;
+  unsigned long long w[kSMaxWorld];
+  bool all = true;
+#pragma unroll
+  for (int r = 0; r < kSMaxWorld; ++r) {
+    w[r] = r < a.world ? ld_tagged_sys(from + (size_t)r * D) : ((unsigned long long)tag << 32);
+    all = all && has_tag(w[r], tag);
+  }
+  const long long t0 = clock64();
+  while (!all && !sh->failed) {
+    __nanosleep(64);
+    all = true;
+#pragma unroll
+    for (int r = 0; r < kSMaxWorld; ++r) {
+      if (r < a.world && !has_tag(w[r], tag)) w[r] = ld_tagged_sys(from + (size_t)r * D);
+      all = all && has_tag(w[r], tag);
+    }
+    if (clock64() - t0 > sh->limit) sh->failed = 1;
+  }
+  float sum = 0.f;
+#pragma unroll
+  for (int r = 0; r < kSMaxWorld; ++r)
+    if (r < a.world) sum += value_of(w[r]);
+  if (!sh->failed) st_tagged(a.summed + (size_t)xpar * D + row, sum, tag);
+}
+
 // Tensor-core variant: every part of row tile `tile` (the routed projections' parts and the shared
 // experts' rows) is in global memory. Sums them in a fixed order -- the parts of a route in block
 // order, the routes in choice order, then the shared experts -- and stores the rows into every
@@ -579,7 +690,7 @@ template <int D, int F>
 __device__ __forceinline__ void finish_row_tile(const StackArgs& a, StackShared* sh, int layer, int par, int xpar, int tile, int first,
                                                 int stride) {
   using S = StackShape<D, F>;
-  (void)layer;
+  const unsigned tag = layer_tag(sh->epoch1, a.n_layers, layer);
   // the routes' activation maxima first (the same for every row), then per row all loads before any arithmetic:
   // this runs in one block per row tile at the very end of a layer, so its round trips to L2 are what it costs
   unsigned amax[kSMaxTopK];
@@ -617,28 +728,11 @@ __device__ __forceinline__ void finish_row_tile(const StackArgs& a, StackShared*
     }
 #pragma unroll
     for (int e = 0; e < kSMaxShared; ++e) total += shared[e];
-    const size_t at = ((size_t)xpar * a.world + a.rank) * D + at_row;
-    for (int r = 0; r < a.world; ++r) a.peer_inbox[r][at] = total;
+    send_row<D>(a, xpar, tag, (int)at_row, total);
   }
+  if (a.world > 1)
+    for (int row = first; row < kTcRows; row += stride) gather_row<D>(a, sh, xpar, tag, tile * kTcRows + row);
 }
-// One thread, after a piece of the layer's output (a block's rows, or a 128-row tile) has been stored
-// into every rank's inbox: count it. One rank: on the layer's counter directly. Several ranks: on a
-// counter of this rank; only the delivery that completes the rank's `pieces` tells the peers, with one
-// system-scope increment each -- hundreds of remote increments on one address per layer cost more
-// than the layer itself.
-__device__ __forceinline__ void count_delivery(const StackArgs& a, int layer, unsigned epoch1, unsigned pieces) {
-  if (a.world > 1) {
-    __threadfence_system();
-    if (atomicAdd(a.local_done + layer, 1u) + 1u == epoch1 * pieces) {
-      __threadfence_system();
-      for (int r = 0; r < a.world; ++r) red_release_sys_add(a.peer_xsync[r] + layer, 1u);
-    }
-  } else {
-    __threadfence();
-    red_release_add(a.xsync + layer, 1u);
-  }
-}
-
 template <int D, int F, bool TC>
 __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_kernel(StackArgs a) {
   using S = StackShape<D, F>;
@@ -678,11 +772,12 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
     sh.sg_done = 0;
     sh.issued = 0;
     sh.routed_layers = 0;
-    for (int i = 0; i < 3; ++i) sh.seen[i] = 0;
+    for (int i = 0; i < 2; ++i) sh.seen[i] = 0;
     for (int i = 0; i < kSMaxShared; ++i) sh.sact_flag[i] = 0;
     for (int i = 0; i < kSMaxTopK; ++i) sh.act_flag[i] = 0;
     sh.failed = 0;
     sh.epoch1 = *a.epoch + 1u;
+    sh.limit = a.wait_limit;
     for (int i = 0; i < 6; ++i) (&sh.done[0][0])[i] = 0;
     mbar_init_fence();
   }
@@ -726,7 +821,7 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
       auto next_slot = [&](unsigned char*& dst, uint64_t*& bar) -> bool {
         const int slot = (int)(issued % kSStages);
         if (sh.failed) return false;
-        if (issued >= kSStages && !mbar_wait(&sh.empty[slot], (uint32_t)((issued / kSStages) - 1) & 1)) {
+        if (issued >= kSStages && !mbar_wait(&sh.empty[slot], (uint32_t)((issued / kSStages) - 1) & 1, sh.limit)) {
           sh.failed = 1;
           return false;
         }
@@ -899,11 +994,7 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
       const unsigned* sync = a.sync + (size_t)layer * kSyncWordsPerLayer;
       // every block resolves the routing for itself (same inputs, same arithmetic, same result): the
       // code stays warm in this SM's instruction cache and nothing has to be published between blocks
-      bool ok = true;
-      if (lane == 0) ok = wait_global(sync + kRouterRows, sh.epoch1 * (unsigned)(a.experts + a.n_shared), &sh);
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) break;
-      stack_router_tail(a, a.layers[layer], layer, &sh);
+      if (!stack_router_tail(a, a.layers[layer], layer, &sh)) break;
       if (!tc && lane == 0) {
         // One lane polls the layer's grid-wide counters for the whole block and raises a flag in shared memory
         // for each: eight polling warps per block crowd the counter's L2 line and hold up its increments.
@@ -914,10 +1005,6 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
         wait_global(sync + kRtGuDone, epoch1 * gridDim.x, &sh);
         __threadfence_block();
         sh.seen[1] = layer + 1;
-        if (a.world > 1) wait_system(a.xsync + layer, epoch1 * (unsigned)a.world, &sh);
-        else wait_global(a.xsync + layer, epoch1 * gridDim.x, &sh);
-        __threadfence_block();
-        sh.seen[2] = layer + 1;
       }
       if (tc && lane == 0 && !sh.failed) {
         // ---- the routed projections on the tensor cores: one thread issues. A unit is 128 weight rows x
@@ -926,7 +1013,7 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
                          int operand_chunk_bytes, uint32_t idesc) {
           const long long t0 = clock64();
           while (*ready <= layer && !sh.failed)
-            if (clock64() - t0 > kWaitLimitCycles) sh.failed = 1;
+            if (clock64() - t0 > sh.limit) sh.failed = 1;
           __threadfence_block();
           tc_fence_after();
           if (ready == &sh.act_ready) INK_TRACE(layer, kTrMmaDownStart);
@@ -985,7 +1072,7 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
         if (ok && lane == 0) ok = tc_wait_issued(i, &sh);
         ok = __all_sync(0xffffffffu, ok);
       }
-      if (ok) ok = mbar_wait(&sh.full[slot], (uint32_t)(i / kSStages) & 1);
+      if (ok) ok = mbar_wait(&sh.full[slot], (uint32_t)(i / kSStages) & 1, sh.limit);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
         sh.failed = 1;
@@ -1064,9 +1151,7 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
       const unsigned epoch1 = sh.epoch1;
       // slot of the ranks' deliveries: alternates with every block of every launch
       const int xpar = (int)(((epoch1 - 1u) * (unsigned)a.n_layers + (unsigned)layer) & 1u);
-      float* inbox = a.inbox + (size_t)xpar * a.world * D;
-      // deliveries of a layer: one per block (CUDA-core variant) or per 128-row tile (tensor-core variant) and rank
-      const unsigned down_target = a.world > 1 ? epoch1 * (unsigned)a.world : epoch1 * (tc ? (unsigned)S::DN_TILES : gridDim.x);
+      const unsigned tag = layer_tag(epoch1, a.n_layers, layer);
       const float x_inverse = sh.x_inverse;
       const bool tracer = (ct == 0);
       if (tracer) INK_TRACE(layer, kTrLayerStart);
@@ -1074,7 +1159,6 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
       if (ct == 0) {
         if (plan.n_sg == 0) red_release_add(sync + kShGuDone, 1u);
         if (plan.n_q == 0 && !tc) red_release_add(sync + kRtGuDone, 1u);   // (the tensor-core path counts tiles)
-        if (!tc && plan.n_sd + plan.n_qd == 0) count_delivery(a, layer, epoch1, gridDim.x);
       }
       // ------------------------------------------------ router rows
       for (int t = first_of(plan.s_r); t < plan.s_sg; t += kSC) {
@@ -1091,14 +1175,11 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
           acc = warp_sum(acc);
           release(slot);
           const int row = plan.r0 + t;
-          if (lane == 0) {
+          if (lane == 0) {   // tagged words: the routing warps of all blocks poll for them
             const float l = round_bf16(acc);
-            a.logits[(size_t)par * total_rows + row] = l;
+            st_tagged(a.logits + (size_t)par * total_rows + row, l, tag);
             if (row < a.experts)
-              a.scores[(size_t)par * a.experts + row] = round_bf16(1.f / (1.f + __expf(-l))) + router_bias[row];
-            __threadfence();
-            const unsigned done = atomicAdd(sync + kRouterRows, 1u) + 1u;
-            (void)done;
+              st_tagged(a.scores + (size_t)par * a.experts + row, round_bf16(1.f / (1.f + __expf(-l))) + router_bias[row], tag);
           }
         } else {
           release(slot);
@@ -1302,10 +1383,6 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
             if (__shfl_sync(0xffffffffu, last, 0)) {
               __threadfence();
               finish_row_tile<D, F>(a, &sh, layer, par, xpar, tile, lane, 32);
-              if (a.world > 1) __threadfence_system();
-              else __threadfence();
-              __syncwarp();
-              if (lane == 0) count_delivery(a, layer, epoch1, (unsigned)S::DN_TILES);
             }
           }
         }
@@ -1404,15 +1481,14 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
         // the last tile is always a routed one.)
         if (last_of_block && !sh.failed) {
           __syncwarp();
-          // deliver this block's rows to every rank (itself included), then count the block there
+          // hand this block's rows over (to every rank, itself included), then sum what the ranks sent for them
           for (int row = lane; row < plan.n_g * S::RT; row += 32) {
             float total = 0.f;
             for (int j = 0; j < n_jobs; ++j) total += sh.contrib[j][row];
-            const size_t at = ((size_t)xpar * a.world + a.rank) * D + (size_t)plan.g0 * S::RT + row;
-            for (int r = 0; r < a.world; ++r) a.peer_inbox[r][at] = total;
+            send_row<D>(a, xpar, tag, plan.g0 * S::RT + row, total);
           }
-          __syncwarp();
-          if (lane == 0) count_delivery(a, layer, epoch1, gridDim.x);
+          if (a.world > 1)
+            for (int row = lane; row < plan.n_g * S::RT; row += 32) gather_row<D>(a, &sh, xpar, tag, plan.g0 * S::RT + row);
         }
       }
       }   // CUDA-core routed down
@@ -1424,26 +1500,13 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
         release(slot);
       }
       if (tracer) INK_TRACE(layer, kTrRtDownDone);
-      // every block of every rank has delivered this layer's rows
-      if (tc) {
-        if (lane == 0) {
-          if (a.world > 1) wait_system(a.xsync + layer, down_target, &sh);
-          else wait_global(a.xsync + layer, down_target, &sh);
-        }
-        __syncwarp();
-      } else {
-        wait_flag(&sh.seen[2], layer, &sh, lane);
-      }
-      if (tracer) INK_TRACE(layer, kTrDownAll);
+      const unsigned long long* summed = a.summed + (size_t)xpar * D;
       if (!a.glue) {
-        // one block only: each block writes the sum over the ranks of its own rows
-        if (!sh.failed)
-          for (int row = ct; row < plan.n_g * S::RT; row += kSC * 32) {
-            const size_t i = (size_t)plan.g0 * S::RT + row;
-            float total = 0.f;
-            for (int r = 0; r < a.world; ++r) total += __ldcg(inbox + (size_t)r * D + i);
-            a.partial[i] = total;
-          }
+        // one block only: each block writes its own rows, summed over the ranks, as they arrive
+        for (int row = ct; row < plan.n_g * S::RT; row += kSC * 32) {
+          const size_t i = (size_t)plan.g0 * S::RT + row;
+          a.partial[i] = wait_tagged(summed + i, tag, &sh);
+        }
         break;
       }
       // the other set of activation maxima is free (its readers finished before this layer's deliveries
@@ -1457,7 +1520,6 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
         // all loads first (they are independent), arithmetic after: one L2 round trip; 16-byte loads of eight
         // consecutive elements keep both the loads and the code that follows short
         const bool live = !sh.failed && holder;
-        const int world = a.world;
         uint4 res[VG], nw[VG];
         float part[VG][8];
 #pragma unroll
@@ -1468,21 +1530,50 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
 #pragma unroll
           for (int k = 0; k < 8; ++k) part[g][k] = 0.f;
         }
-        // every rank's delivery, summed in rank order (same bits on every rank)
-        for (int r = 0; r < world; ++r) {
-          float4 got[VG][2];
+        // The layer's output rows, summed over the ranks, as their owners publish them: every thread polls the
+        // tagged words of its own elements (all of a round in flight together), so a block goes on as soon as
+        // the last row it needs is there -- no counter, no fence.
+        if (live) {
+          unsigned long long w[VG][8];
+          bool all = true;
 #pragma unroll
           for (int g = 0; g < VG; ++g) {
-            const float4* src = reinterpret_cast<const float4*>(inbox + (size_t)r * D) + (size_t)(g * VT + ct) * 2;
-            got[g][0] = live ? __ldcg(src) : make_float4(0.f, 0.f, 0.f, 0.f);
-            got[g][1] = live ? __ldcg(src + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
+            const unsigned long long* src = summed + (size_t)(g * VT + ct) * 8;
+#pragma unroll
+            for (int k = 0; k < 8; k += 2) {
+              unsigned long long pair[2];
+              ld_tagged2(src + k, pair);
+              w[g][k] = pair[0];
+              w[g][k + 1] = pair[1];
+              all = all && has_tag(pair[0], tag) && has_tag(pair[1], tag);
+            }
+          }
+          const long long t0 = clock64();
+          while (!all && !sh.failed) {
+            __nanosleep(100);
+            all = true;
+#pragma unroll
+            for (int g = 0; g < VG; ++g) {
+              const unsigned long long* src = summed + (size_t)(g * VT + ct) * 8;
+#pragma unroll
+              for (int k = 0; k < 8; k += 2) {
+                if (!has_tag(w[g][k], tag) || !has_tag(w[g][k + 1], tag)) {
+                  unsigned long long pair[2];
+                  ld_tagged2(src + k, pair);
+                  w[g][k] = pair[0];
+                  w[g][k + 1] = pair[1];
+                  all = all && has_tag(pair[0], tag) && has_tag(pair[1], tag);
+                }
+              }
+            }
+            if (clock64() - t0 > sh.limit) sh.failed = 1;
           }
 #pragma unroll
-          for (int g = 0; g < VG; ++g) {
-            part[g][0] += got[g][0].x; part[g][1] += got[g][0].y; part[g][2] += got[g][0].z; part[g][3] += got[g][0].w;
-            part[g][4] += got[g][1].x; part[g][5] += got[g][1].y; part[g][6] += got[g][1].z; part[g][7] += got[g][1].w;
-          }
+          for (int g = 0; g < VG; ++g)
+#pragma unroll
+            for (int k = 0; k < 8; ++k) part[g][k] = sh.failed ? 0.f : value_of(w[g][k]);
         }
+        if (tracer) INK_TRACE(layer, kTrDownAll);
         float h[VG][8];
 #pragma unroll
         for (int g = 0; g < VG; ++g) {
@@ -1708,7 +1799,7 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
         wait_routing(layer, &sh);
         const long long t0 = clock64();
         while (sh.sg_done <= layer && !sh.failed)
-          if (clock64() - t0 > kWaitLimitCycles) sh.failed = 1;
+          if (clock64() - t0 > sh.limit) sh.failed = 1;
         __threadfence_block();
       }
       __syncwarp();
@@ -1765,10 +1856,6 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
           if (sh.finisher) {   // every part of the row tile is in: sum and deliver it
             __threadfence();
             finish_row_tile<D, F>(a, &sh, layer, par, xpar, tile, et, 128);
-            if (a.world > 1) __threadfence_system();
-            else __threadfence();
-            epilogue_sync();
-            if (et == 0) count_delivery(a, layer, epoch1, (unsigned)S::DN_TILES);
           }
           u = min(end, (tg + 1) * S::DN_CHUNKS);
         }
@@ -1790,22 +1877,28 @@ template <int D, int F, bool TC>
 static int launch_stack(const StackArgs& a, cudaStream_t stream) {
   using S = StackShape<D, F>;
   constexpr int threads = TC ? kSThreadsTc : kSThreads;
-  static bool configured = false;
-  static int sms = 0;
-  if (!configured) {
+  // The shared-memory opt-in, the cooperative-launch check and the SM count belong to a device, not to
+  // the process: one record per device ordinal (a process may drive several GPUs).
+  constexpr int kMaxDevices = 64;
+  static int sms_of[kMaxDevices] = {};   // 0 = this device is not configured yet
+  int device = 0;
+  cudaGetDevice(&device);
+  INK_REQUIRE(device >= 0 && device < kMaxDevices, kLaunchFailed, "moe_stack: device ordinal %d", device);
+  if (sms_of[device] == 0) {
     cudaError_t e = cudaFuncSetAttribute(moe_stack_kernel<D, F, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM);
     INK_REQUIRE(e == cudaSuccess, kLaunchFailed, "moe_stack: %d bytes of shared memory refused: %s", S::SMEM,
                 cudaGetErrorString(e));
-    INK_PREFER_MAX_SMEM((moe_stack_kernel<D, F, TC>));
-    int device = 0, coop = 0, per_sm = 0;
-    cudaGetDevice(&device);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    cudaFuncSetAttribute(moe_stack_kernel<D, F, TC>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         (int)cudaSharedmemCarveoutMaxShared);
+    int coop = 0, per_sm = 0, count = 0;
+    cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device);
     cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device);
     INK_REQUIRE(coop, kLaunchFailed, "moe_stack: the device cannot launch cooperative kernels");
     e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, moe_stack_kernel<D, F, TC>, threads, S::SMEM);
-    INK_REQUIRE(e == cudaSuccess && per_sm >= 1, kLaunchFailed, "moe_stack: the kernel does not fit on an SM");
-    configured = true;
+    INK_REQUIRE(e == cudaSuccess && per_sm >= 1 && count >= 1, kLaunchFailed, "moe_stack: the kernel does not fit on an SM");
+    sms_of[device] = count;
   }
+  const int sms = sms_of[device];
   const int groups = D / S::RT;
   const int rows_per_block = ((groups + sms - 1) / sms) * S::RT;
   INK_REQUIRE(rows_per_block <= kSMaxRows, kUnsupportedShape, "moe_stack: %d output rows per block", rows_per_block);
@@ -1886,9 +1979,20 @@ static size_t gu_part_bytes(int hidden, int intermediate, int top_k) {
          (size_t)((hidden + kTcChunkK - 1) / kTcChunkK);
 }
 
-// The region other ranks write into: delivered-block counters, then the delivered rows.
+// The region other ranks write into: two sets (alternating from layer to layer) of one slot of
+// `hidden` tagged 8-byte words per rank.
 extern "C" size_t ink_moe_stack_symmetric_bytes(int n_layers, int hidden, int world) {
-  return pad256(sizeof(unsigned) * (size_t)n_layers) + pad256(sizeof(float) * 2 * (size_t)world * hidden);
+  (void)n_layers;
+  return pad256(sizeof(unsigned long long) * 2 * (size_t)world * hidden);
+}
+
+// SM clocks a wait inside the one-launch kernel may take before the launch gives up (default: about a
+// tenth of a second). A diagnostic knob: tests shorten it to see the give-up path without waiting.
+static long long g_stack_wait_limit = kWaitLimitCycles;
+extern "C" int ink_moe_stack_set_wait_limit(long long cycles) {
+  INK_REQUIRE(cycles >= 1000, kBadArgument, "moe_stack: a wait limit of %lld clocks is too short", cycles);
+  g_stack_wait_limit = cycles;
+  return kOk;
 }
 
 extern "C" size_t ink_moe_stack_scratch_bytes(int n_layers, int hidden, int intermediate, int experts, int n_shared,
@@ -1901,14 +2005,13 @@ extern "C" size_t ink_moe_stack_scratch_bytes(int n_layers, int hidden, int inte
   bytes += pad256(dn_part_bytes(hidden, intermediate, top_k));                  // parts of split down tiles
   bytes += pad256(sizeof(float) * 2 * (size_t)n_shared * hidden);               // shared experts' down rows
   bytes += pad256(sizeof(unsigned) * 2 * kSMaxTopK);                            // activation maxima
-  bytes += pad256(sizeof(unsigned) * (size_t)n_layers);                         // deliveries of this rank
   bytes += pad256(sizeof(unsigned) * kTileCounters * (size_t)n_layers);         // tile counters
-  bytes += pad256(sizeof(float) * 2 * (size_t)(experts + n_shared));            // logits
-  bytes += pad256(sizeof(float) * 2 * (size_t)experts);                         // scores
+  bytes += pad256(sizeof(unsigned long long) * 2 * (size_t)(experts + n_shared));   // logits (tagged)
+  bytes += pad256(sizeof(unsigned long long) * 2 * (size_t)experts);            // scores (tagged)
   bytes += pad256(2 * 2 * (size_t)top_k * intermediate);                        // activated
   bytes += pad256(2 * 2 * (size_t)n_shared * intermediate);                     // shared activated
   bytes += pad256(2 * 2 * (size_t)hidden);                                      // residual double buffer
-  bytes += ink_moe_stack_symmetric_bytes(n_layers, hidden, 1);                  // deliveries when there is one rank
+  bytes += pad256(sizeof(unsigned long long) * 2 * (size_t)hidden);             // rows summed over the ranks (tagged)
   bytes += pad256(sizeof(unsigned long long) * (size_t)n_layers * kTraceBlocks * kTraceSlots);   // phase stamps (tracing)
   return bytes;
 }
@@ -1962,27 +2065,21 @@ static int stack_decode(const void* layers, int n_layers, const void* x, void* r
   a.dn_part = (float*)take(dn_part_bytes(hidden, intermediate, top_k));
   a.sd_out = (float*)take(sizeof(float) * 2 * (size_t)n_shared * hidden);
   a.act_amax = (unsigned*)take(sizeof(unsigned) * 2 * kSMaxTopK);
-  a.local_done = (unsigned*)take(sizeof(unsigned) * (size_t)n_layers);
   a.tilesync = (unsigned*)take(sizeof(unsigned) * kTileCounters * (size_t)n_layers);
-  a.logits = (float*)take(sizeof(float) * 2 * (size_t)(experts + n_shared));
-  a.scores = (float*)take(sizeof(float) * 2 * (size_t)experts);
+  a.logits = (unsigned long long*)take(sizeof(unsigned long long) * 2 * (size_t)(experts + n_shared));
+  a.scores = (unsigned long long*)take(sizeof(unsigned long long) * 2 * (size_t)experts);
   a.activated = (uint16_t*)take(2 * 2 * (size_t)top_k * intermediate);
   a.shared_activated = (uint16_t*)take(2 * 2 * (size_t)n_shared * intermediate);
   a.residual = (uint16_t*)take(2 * 2 * (size_t)hidden);
-  char* own_region = take(ink_moe_stack_symmetric_bytes(n_layers, hidden, 1));
-  for (int r = 0; r < kSMaxWorld; ++r) {
-    a.peer_inbox[r] = nullptr;
-    a.peer_xsync[r] = nullptr;
-  }
-  const size_t counters = pad256(sizeof(unsigned) * (size_t)n_layers);
-  for (int r = 0; r < world; ++r) {
-    char* region = world == 1 ? own_region : (char*)(uintptr_t)peer_regions[r];
+  a.summed = (unsigned long long*)take(sizeof(unsigned long long) * 2 * (size_t)hidden);
+  a.wait_limit = g_stack_wait_limit;
+  for (int r = 0; r < kSMaxWorld; ++r) a.peer_inbox[r] = nullptr;
+  for (int r = 0; r < world && world > 1; ++r) {
+    char* region = (char*)(uintptr_t)peer_regions[r];
     INK_REQUIRE(region != nullptr && aligned16(region), kBadArgument, "moe_stack: bad region for rank %d", r);
-    a.peer_xsync[r] = (unsigned*)region;
-    a.peer_inbox[r] = (float*)(region + counters);
+    a.peer_inbox[r] = (unsigned long long*)region;
   }
-  a.xsync = a.peer_xsync[rank];
-  a.inbox = a.peer_inbox[rank];
+  a.inbox = world > 1 ? a.peer_inbox[rank] : nullptr;
   // INKLING_STACK_TRACE=1: blocks stamp their phase boundaries (global nanosecond timer) into the
   // tail of the scratch, where ink_moe_stack_trace_offset() says
   const char* tracing = getenv("INKLING_STACK_TRACE");

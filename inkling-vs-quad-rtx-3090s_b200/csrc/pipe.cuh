@@ -32,11 +32,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait: about a tenth of a second of SM clocks, then give up.
 constexpr long long kWaitLimitCycles = 200000000LL;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, long long limit = kWaitLimitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (!mbar_try_wait(bar, parity))
-    if (clock64() - t0 > kWaitLimitCycles) return false;
+    if (clock64() - t0 > limit) return false;
   return true;
 }
 // global -> shared bulk copy; dst, src 16-byte aligned, bytes a multiple of 16

@@ -8,6 +8,7 @@
 #include "../../include/inkling_b200.h"
 #include "common.cuh"
 #include "decode_args.cuh"
+#include "stream_math.cuh"
 
 namespace ink {
 
@@ -23,24 +24,6 @@ struct RowMap {
   static constexpr int PASSES = (kBatchLoads / CPL) > 0 ? (kBatchLoads / CPL) : 1;  // passes per batch
   static constexpr int ROWS_PER_BATCH = PASSES * RPP;
 };
-
-// 32 weights x 32 FP16 activations with their two block scales -> FP32
-__device__ __forceinline__ float dot32_nvfp4(const uint4& q, uint32_t scale_pair, const uint32_t* x) {
-  uint32_t h[4];
-  uint32_t a0 = 0u, a1 = 0u;
-  e2m1x8_to_f16x2(q.x, h);
-  a0 = hfma2(h[0], x[0], a0); a0 = hfma2(h[1], x[1], a0); a0 = hfma2(h[2], x[2], a0); a0 = hfma2(h[3], x[3], a0);
-  e2m1x8_to_f16x2(q.y, h);
-  a0 = hfma2(h[0], x[4], a0); a0 = hfma2(h[1], x[5], a0); a0 = hfma2(h[2], x[6], a0); a0 = hfma2(h[3], x[7], a0);
-  e2m1x8_to_f16x2(q.z, h);
-  a1 = hfma2(h[0], x[8], a1); a1 = hfma2(h[1], x[9], a1); a1 = hfma2(h[2], x[10], a1); a1 = hfma2(h[3], x[11], a1);
-  e2m1x8_to_f16x2(q.w, h);
-  a1 = hfma2(h[0], x[12], a1); a1 = hfma2(h[1], x[13], a1); a1 = hfma2(h[2], x[14], a1); a1 = hfma2(h[3], x[15], a1);
-  const uint32_t s = e4m3x2_to_f16x2((uint16_t)scale_pair);
-  const float b0 = f16lo_to_f32(a0) + f16hi_to_f32(a0);
-  const float b1 = f16lo_to_f32(a1) + f16hi_to_f32(a1);
-  return fmaf(f16lo_to_f32(s), b0, f16hi_to_f32(s) * b1);
-}
 
 // 8 BF16 weights x 8 FP32 activations
 __device__ __forceinline__ float dot8_bf16(const uint4& q, const float4& xa, const float4& xb, float acc) {
@@ -115,7 +98,7 @@ __device__ __forceinline__ void warp_rows_nvfp4(const uint8_t* __restrict__ W, c
   for (int p = 0; p < M::PASSES; ++p) {
     float acc = 0.f;
 #pragma unroll
-    for (int j = 0; j < M::CPL; ++j) acc += dot32_nvfp4(q[p][j], sc[p][j], xr[j]);
+    for (int j = 0; j < M::CPL; ++j) acc += dot32(q[p][j], sc[p][j], xr[j]);
     result[p] = group_sum<M::LPR>(acc);
   }
 }
@@ -406,6 +389,107 @@ __global__ void __launch_bounds__(kDownThreads) down_kernel(DecodeArgs a, int ti
     if (warp_row0 + i < d) a.output[(size_t)token * d + warp_row0 + i] = s_total[warp][i];
 }
 
+// ============================================== BF16 expert banks (pointer stride 2)
+// The unquantised expert layer (the reference's routed_decode.cu built with QUANT=0, :85-101):
+// the same two kernels over BF16 rows, no scales. A route's table row is (gate_up_proj, down_proj).
+constexpr int kBankBf16 = 2;
+constexpr int kBf16PairsPerWarp = 2;
+
+template <int K>
+__global__ void __launch_bounds__(kGateUpThreads) gate_up_bf16_kernel(DecodeArgs a, int tiles) {
+  __shared__ __align__(16) float s_x[K];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int route = blockIdx.x / tiles, tile = blockIdx.x % tiles;
+  const int f = a.intermediate;
+  const int64_t expert = a.indices[route];
+  if (expert < 0 || expert > a.max_expert) {
+    if (threadIdx.x == 0 && a.status) atomicOr(a.status, kFlagExpertOutOfRange);
+    return;
+  }
+  const uint16_t* W = reinterpret_cast<const uint16_t*>(a.pointers[expert * kBankBf16]);
+  if (W == nullptr) return;
+  const uint16_t* x = a.x + (size_t)(route / a.top_k) * K;
+  for (int i = threadIdx.x; i < K / 2; i += blockDim.x) {
+    const uint32_t v = reinterpret_cast<const uint32_t*>(x)[i];
+    s_x[2 * i] = bf16lo(v);
+    s_x[2 * i + 1] = bf16hi(v);
+  }
+  __syncthreads();
+  uint16_t* y = a.activated + (size_t)route * f;
+#pragma unroll 1
+  for (int i = 0; i < kBf16PairsPerWarp; ++i) {
+    const int j = (tile * kGateUpWarps + warp) * kBf16PairsPerWarp + i;
+    if (j >= f) break;
+    float g, u;
+    // rows interleave: gate = row 2j, up = row 2j + 1
+    warp_pair_bf16<K>(W + (size_t)(2 * j) * K, W + (size_t)(2 * j + 1) * K, s_x, &g, &u);
+    if (lane == 0) y[j] = (uint16_t)f32_to_bf16_bits(silu_mul(g, u));
+  }
+}
+
+// dynamic shared memory: top_k FP32 vectors of K
+template <int K>
+__global__ void __launch_bounds__(kDownThreads) down_bf16_kernel(DecodeArgs a, int tiles, int rows_per_warp) {
+  extern __shared__ __align__(16) unsigned char s_dyn[];
+  float* s_act = reinterpret_cast<float*>(s_dyn);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int token = blockIdx.x / tiles, tile = blockIdx.x % tiles;
+  const int d = a.hidden;
+  for (int i = threadIdx.x; i < a.top_k * (K / 2); i += blockDim.x) {
+    const uint32_t v = reinterpret_cast<const uint32_t*>(a.activated + (size_t)token * a.top_k * K)[i];
+    s_act[2 * i] = bf16lo(v);
+    s_act[2 * i + 1] = bf16hi(v);
+  }
+  __syncthreads();
+  const int row0 = (tile * kDownWarps + warp) * rows_per_warp;
+#pragma unroll 1
+  for (int i = 0; i < rows_per_warp; ++i) {
+    const int row = row0 + i;
+    if (row >= d) break;
+    float total = 0.f;
+#pragma unroll 1
+    for (int choice = 0; choice < a.top_k; ++choice) {
+      const int route = token * a.top_k + choice;
+      const int64_t expert = a.indices[route];
+      if (expert < 0 || expert > a.max_expert) {
+        if (lane == 0 && row == 0 && a.status) atomicOr(a.status, kFlagExpertOutOfRange);
+        continue;
+      }
+      const uint16_t* W = reinterpret_cast<const uint16_t*>(a.pointers[expert * kBankBf16 + 1]);
+      if (W == nullptr) continue;
+      const float down = round_bf16(warp_row_bf16<K>(W + (size_t)row * K, s_act + (size_t)choice * K));
+      total += round_bf16(down * bf16_to_f32(a.weights[route]));
+    }
+    if (lane == 0) a.output[(size_t)token * d + row] = total;
+  }
+}
+
+template <int K>
+static int launch_gate_up_bf16(const DecodeArgs& a, cudaStream_t stream) {
+  const int per_block = kGateUpWarps * kBf16PairsPerWarp;
+  const int tiles = (a.intermediate + per_block - 1) / per_block;
+  gate_up_bf16_kernel<K><<<(unsigned)(a.tokens * a.top_k * tiles), kGateUpThreads, 0, stream>>>(a, tiles);
+  INK_CHECK_LAUNCH("gate_up (BF16 banks)");
+  return kOk;
+}
+
+template <int K>
+static int launch_down_bf16(const DecodeArgs& a, cudaStream_t stream) {
+  const int rows_per_warp = 4, per_block = kDownWarps * rows_per_warp;
+  const int tiles = (a.hidden + per_block - 1) / per_block;
+  const size_t smem = (size_t)a.top_k * K * 4;
+  static thread_local size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(down_bf16_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    INK_REQUIRE(e == cudaSuccess, kLaunchFailed, "down (BF16 banks): %zu bytes of shared memory refused: %s", smem,
+                cudaGetErrorString(e));
+    configured = smem;
+  }
+  down_bf16_kernel<K><<<(unsigned)(a.tokens * tiles), kDownThreads, smem, stream>>>(a, tiles, rows_per_warp);
+  INK_CHECK_LAUNCH("down (BF16 banks)");
+  return kOk;
+}
+
 // ---------------------------------------------------------------- launchers
 template <int K>
 static int launch_gate_up(const DecodeArgs& a, cudaStream_t stream) {
@@ -457,6 +541,16 @@ static int dispatch_gate_up(const DecodeArgs& a, cudaStream_t stream) {
 static int dispatch_down(const DecodeArgs& a, cudaStream_t stream) {
   INK_DISPATCH_WIDTH(a.intermediate, launch_down)
   set_error("down: intermediate=%d unsupported (power of two, 64..4096)", a.intermediate);
+  return kUnsupportedShape;
+}
+static int dispatch_gate_up_bf16(const DecodeArgs& a, cudaStream_t stream) {
+  INK_DISPATCH_WIDTH(a.hidden, launch_gate_up_bf16)
+  set_error("gate_up (BF16 banks): hidden=%d unsupported (power of two, 64..4096)", a.hidden);
+  return kUnsupportedShape;
+}
+static int dispatch_down_bf16(const DecodeArgs& a, cudaStream_t stream) {
+  INK_DISPATCH_WIDTH(a.intermediate, launch_down_bf16)
+  set_error("down (BF16 banks): intermediate=%d unsupported (power of two, 64..4096)", a.intermediate);
   return kUnsupportedShape;
 }
 
@@ -551,8 +645,16 @@ extern "C" int ink_routed_decode(const void* x, const int64_t* indices, const vo
                                  const int64_t* pointers, void* activated, float* output, int tokens, int top_k,
                                  int hidden, int intermediate, int max_expert, int quantized, int32_t* status,
                                  ink_stream_t stream) {
-  INK_REQUIRE(quantized == 1, kUnsupportedShape,
-              "routed_decode: only NVFP4 banks (quantized=1) are built; BF16 expert banks are not");
+  INK_REQUIRE(quantized == 0 || quantized == 1, kBadArgument, "routed_decode: quantized=%d", quantized);
+  if (quantized == 0) {
+    // BF16 banks: pointer table [expert][2] = (gate_up_proj BF16 [2f, d], down_proj BF16 [d, f])
+    DecodeArgs a = make_decode_args(x, indices, weights, pointers, activated, nullptr, nullptr, nullptr, nullptr, nullptr,
+                                    output, tokens, top_k, 0, hidden, intermediate, max_expert, status);
+    if (int rc = check_decode(a, false)) return rc;
+    if (tokens == 0) return kOk;
+    if (int rc = dispatch_gate_up_bf16(a, (cudaStream_t)stream)) return rc;
+    return dispatch_down_bf16(a, (cudaStream_t)stream);
+  }
   return ink_moe_decode(x, indices, weights, pointers, activated, nullptr, nullptr, nullptr, nullptr, nullptr,
                         output, tokens, top_k, 0, hidden, intermediate, max_expert, status, stream);
 }

@@ -412,7 +412,10 @@ constexpr size_t kStaticRouterBytes = 256 + 2 * sizeof(float) * kStaticRouterTok
 static __device__ __align__(256) unsigned char g_static_router_scratch[kStaticRouterBytes];
 
 constexpr int kStaticMaxDevices = 64;
-static void* g_static_router_ptr[kStaticMaxDevices];   // device address of the array, per device ordinal
+// Device address of the array, per device ordinal. Written without a lock: two host threads that
+// make the first call on a device together both look the address up and store the same value.
+// The address stays valid for the life of the process as long as the device is not reset.
+static void* g_static_router_ptr[kStaticMaxDevices];
 
 extern "C" int ink_router_forward_static(const void* x, const void* weight, const float* bias,
                                          const void* global_scale, float route_scale, int tokens, int hidden,

@@ -2,8 +2,8 @@
 routed-expert path: same names, same call signatures, sm_100a library underneath."""
 from .expert_planner import expert_copy, expert_plan
 from .grouped_experts import expert_bank_names, expert_gemm, expert_reduce
-from .routed_decode import add_rmsnorm, moe_decode, routed_decode
-from .stack import StackDescriptor, stack_supported
+from .routed_decode import add_rmsnorm, moe_decode, routed_decode, short_conv
+from .stack import StackDescriptor, set_wait_limit, stack_supported
 from .router import router_forward, router_forward_static, router_plan_forward, router_workspace
 
 __all__ = [
@@ -16,6 +16,8 @@ __all__ = [
     "moe_decode",
     "routed_decode",
     "StackDescriptor",
+    "set_wait_limit",
+    "short_conv",
     "stack_supported",
     "router_forward",
     "router_forward_static",

@@ -30,6 +30,7 @@ _SIGNATURES = {
     "ink_moe_gate_up": (I, [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P, P]),
     "ink_moe_down": (I, [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P, P]),
     "ink_add_rmsnorm": (I, [P, P, P, F, P, I, I, P]),
+    "ink_short_conv": (I, [P, I, P, P, P, P, I, I, I, P]),
     "ink_expert_gemm_scratch_bytes": (Z, [I]),
     "ink_expert_gemm": (I, [P, I, P, P, P, P, P, I, I, I, I, I, I, I, P, Z, P, P]),
     "ink_expert_reduce": (I, [P, P, P, P, P, I, I, I, I, I, P]),
@@ -40,6 +41,7 @@ _SIGNATURES = {
     "ink_moe_stack_decode": (I, [P, I, P, P, P, P, I, F, I, I, I, I, I, P, Z, P, P]),
     "ink_moe_stack_symmetric_bytes": (Z, [I, I, I]),
     "ink_moe_stack_decode_tp": (I, [P, I, P, P, P, P, I, F, I, I, I, I, I, P, Z, I, I, P, P, P]),
+    "ink_moe_stack_set_wait_limit": (I, [ctypes.c_longlong]),
 }
 
 

@@ -73,3 +73,23 @@ def add_rmsnorm(partial, residual, weight, eps: float, normed) -> None:
     _abi.require_cuda(partial, residual, weight, normed)
     _abi.check(_abi.lib().ink_add_rmsnorm(partial.data_ptr(), residual.data_ptr(), weight.data_ptr(), float(eps),
                                           normed.data_ptr(), tokens, hidden, _abi.stream()))
+
+
+def short_conv(x, weight, history, residual=None):
+    """One decode token through the short convolution, as the reference's
+    kernels/decode.py:115-146 `short_conv`: x [bs, 1, d] BF16 (or FP32: the block's all-reduced
+    output, rounded to BF16 first), weight FP32 [d, 1, K], history FP32 [bs, d, K] shifted in
+    place, residual [bs, 1, d] BF16 or None. Returns BF16 [bs, 1, d]."""
+    bs, _, d = x.shape
+    k = weight.shape[-1]
+    assert x.stride(-1) == 1 and x.is_contiguous() and history.is_contiguous() and weight.is_contiguous()
+    assert x.dtype in (torch.bfloat16, torch.float32) and weight.dtype == history.dtype == torch.float32
+    assert history.shape == (bs, d, k) and weight.shape == (d, 1, k)
+    if residual is not None:
+        assert residual.dtype == torch.bfloat16 and residual.shape == x.shape and residual.is_contiguous()
+    y = torch.empty((bs, 1, d), dtype=torch.bfloat16, device=x.device)
+    _abi.require_cuda(x, weight, history, residual, y)
+    _abi.check(_abi.lib().ink_short_conv(x.data_ptr(), int(x.dtype == torch.float32), weight.data_ptr(),
+                                         history.data_ptr(), _abi.ptr(residual), y.data_ptr(), bs, d, k,
+                                         _abi.stream()))
+    return y

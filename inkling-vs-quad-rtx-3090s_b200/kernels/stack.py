@@ -20,6 +20,12 @@ def tensor_cores_requested() -> bool:
     return os.environ.get("INKLING_STACK_TENSOR_CORES", "0") == "1"
 
 
+def set_wait_limit(cycles: int) -> None:
+    """SM clocks a wait inside the one-launch kernel may take before the launch gives up
+    (ink_moe_stack_set_wait_limit). Default 200 000 000."""
+    _abi.check(_abi.lib().ink_moe_stack_set_wait_limit(int(cycles)))
+
+
 def stack_supported(hidden: int, intermediate: int, experts: int, n_shared: int, top_k: int) -> bool:
     return ((hidden, intermediate) in BUILT_SHAPES and experts <= 512 and top_k <= 8 and n_shared <= 2
             and top_k <= experts)
@@ -60,7 +66,7 @@ class StackDescriptor:
         size = _abi.lib().ink_moe_stack_scratch_bytes(self.n_layers, hidden, intermediate, experts, n_shared, top_k)
         self.scratch = torch.zeros(size, dtype=torch.uint8, device=device)   # counters start at zero, then only grow
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
-        self.rank, self.world, self.peer_regions, self.symmetric = 0, 1, None, None
+        self.rank, self.world, self.peer_regions, self.symmetric, self.group = 0, 1, None, None, None
         if group is not None and torch.distributed.is_initialized() and torch.distributed.get_world_size(group) > 1:
             self._join(group, device)
 
@@ -71,6 +77,7 @@ class StackDescriptor:
 
         import torch.distributed._symmetric_memory as symm_mem
 
+        self.group = group
         self.rank = torch.distributed.get_rank(group)
         self.world = torch.distributed.get_world_size(group)
         size = _abi.lib().ink_moe_stack_symmetric_bytes(self.n_layers, self.hidden, self.world)
@@ -100,14 +107,49 @@ class StackDescriptor:
                                                           self.status.data_ptr(), _abi.stream()))
 
     def check_status(self) -> None:
-        """Host read (synchronises): raises if a bounded wait inside the kernel gave up."""
-        flags = int(self.status.item())
+        """Host read (synchronises): raises if a bounded wait inside the kernel gave up, after
+        putting the scratch back into its initial state so that the next launch is sound.
+
+        With several ranks this is a COLLECTIVE: every rank must call it at the same point. The
+        ranks agree on whether anyone failed (an abandoned launch on one rank leaves every rank's
+        launch counts and tags out of step), and if so all of them zero scratch and symmetric
+        region between two barriers, so that nobody stores into a region that is being cleared."""
+        flags = self.status.clone()
+        if self.world > 1:
+            torch.distributed.all_reduce(flags, op=torch.distributed.ReduceOp.BOR, group=self.group)
+        flags = int(flags.item())
         self.status.zero_()
         if flags & 2:
-            self.scratch.zero_()   # the counters are inconsistent after an abandoned launch
+            if self.world > 1:
+                torch.cuda.synchronize()
+                torch.distributed.barrier(self.group)   # no launch of any rank is still storing
+            self.scratch.zero_()   # counters, launch count and tagged words start over
             if self.symmetric is not None:
                 self.symmetric.zero_()
+            if self.world > 1:
+                torch.cuda.synchronize()
+                torch.distributed.barrier(self.group)   # every region is clean before anyone launches again
             raise RuntimeError("moe_stack: a bounded wait inside the kernel timed out; the output is invalid")
+
+    def seed_launch_count(self, launches: int) -> None:
+        """Test hook: make the scratch look as if `launches` launches had already run (launch
+        count and the two grid-wide counters of every block, which grow by one per thread block
+        and launch), so that the wrap of the 32-bit counts can be reached without running
+        2^32 / 148 launches first. CUDA-core variant on one GPU only; synchronises."""
+        assert self.bank_maps is None and self.world == 1
+        blocks = torch.cuda.get_device_properties(self.scratch.device).multi_processor_count
+        words = self.scratch.view(torch.int32)
+        sync_words = 8 * self.n_layers                       # [n_layers][8] counters at the start of the scratch
+        epoch_at = (sync_words * 4 + 255) // 256 * 256 // 4  # the launch count follows, 256-byte aligned
+
+        def as_i32(v: int) -> int:
+            v &= 0xFFFFFFFF
+            return v - (1 << 32) if v >= 1 << 31 else v
+
+        torch.cuda.synchronize()
+        words[:sync_words].view(self.n_layers, 8)[:, 0:2] = as_i32(launches * blocks)
+        words[epoch_at] = as_i32(launches)
+        torch.cuda.synchronize()
 
     TRACE_SLOTS = ("layer_start", "router_rows_done", "shared_gate_up_done", "routed_gate_up_done",
                    "shared_gate_up_everywhere", "shared_down_done", "routed_gate_up_everywhere", "activations_staged",

@@ -47,18 +47,21 @@ class ResidentExperts(nn.Module):
     `weights` is keyed by global expert id, each value the bank dictionary
     {gate_up_proj, gate_up_proj_scale, gate_up_proj_scale2, down_proj, down_proj_scale,
     down_proj_scale2} of CUDA tensors already sliced for this rank (slices of every
-    expert on the FFN width), inputs replicated across ranks.
+    expert on the FFN width), inputs replicated across ranks. With `quantized=False` the
+    banks are the unquantised layer's {gate_up_proj BF16 [2f, d] (rows interleave gate and
+    up), down_proj BF16 [d, f]} and the pointer table has stride 2
+    (kernels/grouped_experts.py:9-22); that layer runs one matrix-vector product per route
+    at every token count.
     """
 
     def __init__(self, hidden_dim: int, intermediate_dim: int, device_mesh, weights: dict, quantized: bool = True,
                  dtype=torch.bfloat16):
         super().__init__()
-        if not quantized:
-            raise RuntimeError("ResidentExperts: only NVFP4 banks are built (the BF16 expert layer is not)")
         self.device_mesh = device_mesh
         self.weights = weights  # keeps the allocations alive
-        self.hidden_dim, self.intermediate_dim, self.dtype, self.quantized = hidden_dim, intermediate_dim, dtype, True
-        names = expert_bank_names(True)
+        self.hidden_dim, self.intermediate_dim, self.dtype = hidden_dim, intermediate_dim, dtype
+        self.quantized = bool(quantized)
+        names = expert_bank_names(self.quantized)
         self.stride = len(names)
         ids = sorted(weights)
         self.start, self.local, self.max_expert = ids[0], len(ids), ids[-1]
@@ -66,18 +69,19 @@ class ResidentExperts(nn.Module):
         first = weights[ids[0]]
         self.device = first[names[0]].device
         assert all(w.is_contiguous() and w.is_cuda for e in weights.values() for w in e.values())
-        assert first["gate_up_proj"].shape == (2 * intermediate_dim, hidden_dim // 2)
-        assert first["down_proj"].shape == (hidden_dim, intermediate_dim // 2)
+        packed = 2 if self.quantized else 1
+        assert first["gate_up_proj"].shape == (2 * intermediate_dim, hidden_dim // packed)
+        assert first["down_proj"].shape == (hidden_dim, intermediate_dim // packed)
+        assert first["gate_up_proj"].dtype == (torch.uint8 if self.quantized else torch.bfloat16)
         self.num_slots = 0
         i32 = dict(dtype=torch.int32, device=self.device)
         self.sources = torch.tensor([[weights[e][n].data_ptr() for n in names] for e in ids],
                                     dtype=torch.int64, device=self.device)
         # banks of one kind evenly spaced in memory (one allocation per kind, say): (address of the first,
         # byte distance) per kind, for the TMA descriptors of the one-launch kernel; otherwise None
-        self.bank_layout = self._even_spacing([[weights[e][n].data_ptr() for e in ids] for n in
-                                               ("gate_up_proj", "gate_up_proj_scale", "down_proj", "down_proj_scale")],
-                                              [first[n].numel() * first[n].element_size() for n in
-                                               ("gate_up_proj", "gate_up_proj_scale", "down_proj", "down_proj_scale")])
+        kinds = ("gate_up_proj", "gate_up_proj_scale", "down_proj", "down_proj_scale")
+        self.bank_layout = self._even_spacing([[weights[e][n].data_ptr() for e in ids] for n in kinds],
+                                              [first[n].numel() * first[n].element_size() for n in kinds]) if self.quantized else None
         self.resident = torch.ones(self.local, **i32)
         self.destinations = torch.zeros((0, self.stride), dtype=torch.int64, device=self.device)
         self.slot_experts = torch.full((0,), -1, **i32)
@@ -122,8 +126,8 @@ class ResidentExperts(nn.Module):
         expert_copy[(128, 0)](self.sources, self.destinations, self.copy_experts, (), self.stride, 1024, 128)
 
     def grouped_supported(self) -> bool:
-        """The tensor-core path needs both contraction widths to be multiples of 128."""
-        return self.hidden_dim % 128 == 0 and self.intermediate_dim % 128 == 0
+        """The tensor-core path takes NVFP4 banks whose contraction widths are multiples of 128."""
+        return self.quantized and self.hidden_dim % 128 == 0 and self.intermediate_dim % 128 == 0
 
     def _project(self, x, indices, weights, output) -> None:
         """GEMV per route up to MATVEC_TOKENS tokens, grouped tensor-core GEMMs above
@@ -145,7 +149,7 @@ class ResidentExperts(nn.Module):
         for t0 in range(0, tokens, MATVEC_TOKENS):
             t1 = min(tokens, t0 + MATVEC_TOKENS)
             routed_decode(x[t0:t1], indices[t0:t1], weights[t0:t1], self.pointers,
-                          self.activated[t0 * indices.shape[1]:], output[t0:t1], self.max_expert, True,
+                          self.activated[t0 * indices.shape[1]:], output[t0:t1], self.max_expert, self.quantized,
                           status=self.status)
 
     def forward(self, hidden_states, top_k_index, top_k_weights):
@@ -158,9 +162,13 @@ class ResidentExperts(nn.Module):
 
     def check_status(self) -> None:
         """Host read (synchronises): raises if any call since the last check routed to an
-        expert id outside [0, max_expert]. Call outside graph capture."""
+        expert id outside [0, max_expert] (bit 0 of the status word), or if a bounded wait
+        inside a streaming or grouped kernel gave up (bit 1: that call's output is partial).
+        Call outside graph capture."""
         flags = int(self.status.item())
         self.status.zero_()
+        if flags & 2:
+            raise RuntimeError("ResidentExperts: a bounded wait inside a kernel timed out; the output of that call is invalid")
         if flags & 1:
             raise RuntimeError("ResidentExperts: a route named an expert id outside the pointer table")
 
@@ -179,6 +187,7 @@ class FusedMoE(nn.Module):
         self.route_scale, self.top_k = float(route_scale), top_k
         self.shared_gate, self.shared_up, self.shared_down = shared_gate, shared_up, shared_down
         self.n_shared = shared_gate.shape[0]
+        assert experts.quantized, "FusedMoE takes NVFP4 experts; an unquantised layer keeps its own block around ResidentExperts"
         self.experts = experts
         self.device_mesh = device_mesh
         self._tokens = 0
@@ -240,16 +249,6 @@ class FusedMoE(nn.Module):
         flat = hidden_states.reshape(-1, shape[-1]).contiguous()
         return self.forward_partial(flat).to(hidden_states.dtype).view(shape)
 
-    def _shared_experts(self, flat, gammas):
-        """my_inkling/model.py:192-226 with torch's BF16 GEMMs: gate/up, silu * up * gamma, down,
-        FP32 sum over the shared experts, one BF16 rounding."""
-        h = flat.unsqueeze(0).expand(self.n_shared, -1, -1)
-        gate = torch.bmm(h, self.shared_gate.transpose(1, 2))
-        up = torch.bmm(h, self.shared_up.transpose(1, 2))
-        activated = torch.nn.functional.silu(gate) * up * gammas.T.unsqueeze(-1)
-        down = torch.bmm(activated, self.shared_down.transpose(1, 2))
-        return down.float().sum(dim=0).to(flat.dtype)
-
     def forward_partial(self, flat):
         """flat BF16 [t, d] -> the all-reduced FP32 layer output [t, d] (a view of the
         module's own buffer, overwritten by the next call)."""
@@ -280,8 +279,10 @@ def apply_resident_plan(model: nn.Module, device_mesh, expert_state_dict: dict) 
     `expert_state_dict` by ResidentExperts over this rank's banks."""
     for name, module in list(model.named_modules()):
         if name in expert_state_dict and hasattr(module, "intermediate_dim") and hasattr(module, "hidden_dim"):
+            banks = expert_state_dict[name]
+            quantized = "gate_up_proj_scale" in next(iter(banks.values()))   # offloaded_experts.py:333
             model.set_submodule(name, ResidentExperts(module.hidden_dim, module.intermediate_dim, device_mesh,
-                                                      expert_state_dict[name]))
+                                                      banks, quantized))
     return model
 
 

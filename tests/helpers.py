@@ -15,6 +15,15 @@ def max_rel(actual, expected) -> float:
     return float((actual - expected).abs().max() / expected.abs().max().clamp_min(1e-30))
 
 
+def rel_floor(actual, expected, floor_fraction: float = 0.05) -> float:
+    """max_i |a_i - e_i| / max(|e_i|, floor): the per-element relative error with an absolute
+    floor of `floor_fraction` of the largest expected magnitude (elements near zero are
+    measured against the floor instead of against themselves)."""
+    actual, expected = torch.as_tensor(actual).double().cpu(), torch.as_tensor(expected).double().cpu()
+    floor = floor_fraction * expected.abs().max().clamp_min(1e-30)
+    return float(((actual - expected).abs() / expected.abs().clamp_min(floor)).max())
+
+
 def bf16_ulps(actual, expected) -> torch.Tensor:
     """Distance in BF16 units in the last place between two BF16 tensors."""
     a = actual.cpu().to(BF16).view(torch.int16).to(torch.int32)

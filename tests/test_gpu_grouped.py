@@ -5,7 +5,7 @@ import pytest
 import torch
 
 import cases
-from helpers import BF16, banks_to_device, layer_on_device, max_rel, pointer_table
+from helpers import BF16, banks_to_device, layer_on_device, max_rel, pointer_table, rel_floor
 from oracle import moe as oracle_moe
 
 pytestmark = pytest.mark.gpu
@@ -108,3 +108,12 @@ def test_batched_decode_64_tokens_zipf_at_full_shapes(ib, device):
     assert torch.isfinite(grouped).all()
     assert max_rel(grouped, gemv) <= TOL
     experts.check_status()
+    # and against the float64 oracle on a few tokens (their experts' banks copied to the host)
+    for token in (0, 41):
+        ids = idx[token].cpu()
+        cpu_banks = {int(e): {n: t.cpu() for n, t in banks.weights[int(e)].items()} for e in ids.tolist()}
+        want = oracle_moe.routed_experts_fp32(x[token:token + 1].cpu(), ids.view(1, -1), w[token:token + 1].cpu(), cpu_banks)
+        for got in (grouped[token:token + 1], gemv[token:token + 1]):
+            assert max_rel(got, want) <= TOL
+            assert rel_floor(got, want) <= 0.2
+        del cpu_banks

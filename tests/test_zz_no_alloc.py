@@ -73,3 +73,40 @@ def test_static_scratch_router_refuses_what_does_not_fit():
         p["global_scale"].to(device).data_ptr(), ctypes.c_float(8.0), t, x.shape[1], p["experts"], ns, k, None,
         dummy.data_ptr(), idx.data_ptr(), dummy.data_ptr(), torch.cuda.current_stream().cuda_stream)
     assert rc < 0 and b"at most 8" in lib.ink_last_error()
+
+
+def test_static_scratch_router_allocates_nothing_and_takes_its_largest_case():
+    """Free device memory is the same before and after a warm call (nothing was allocated on the
+    way), through the Python mirror of the entry point, at the limits it accepts: 8 tokens,
+    no logits output; and a router with more rows than the array holds is refused."""
+    import inkling_b200
+    from inkling_b200.kernels import _abi
+
+    lib = _abi.lib()
+    device = torch.device("cuda", 0)
+    gen = torch.Generator().manual_seed(22)
+    p = dict(experts=256, n_shared=2, top_k=6, route_scale=8.0)
+    weight = (torch.randn(258, 4096, generator=gen) * 0.02).to(BF16).to(device)
+    bias = (torch.randn(256, generator=gen) * 0.05).to(device)
+    scale = torch.ones(1, dtype=BF16, device=device)
+    x = torch.randn(8, 4096, generator=gen).to(BF16).to(device)
+    outs = [(torch.empty(8, 6, dtype=BF16, device=device), torch.full((8, 6), -1, dtype=torch.int64, device=device),
+             torch.empty(8, 2, dtype=BF16, device=device)) for _ in range(2)]
+    workspace = inkling_b200.kernels.router_workspace(8, 258, device)
+    inkling_b200.kernels.router_forward_static(x, weight, bias, scale, 8.0, 6, 2, *outs[0])   # warm: address looked up
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info(device)
+    inkling_b200.kernels.router_forward_static(x, weight, bias, scale, 8.0, 6, 2, *outs[0])
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info(device)
+    assert free_after == free_before
+    inkling_b200.kernels.router_forward(x, weight, bias, scale, 8.0, 6, 2, *outs[1], workspace)
+    torch.cuda.synchronize()
+    for got, want in zip(outs[0], outs[1]):
+        assert torch.equal(got, want)
+    # 545 router rows: more than the array holds
+    wide = torch.zeros(545, 64, dtype=BF16, device=device)
+    rc = lib.ink_router_forward_static(
+        x.data_ptr(), wide.data_ptr(), bias.data_ptr(), scale.data_ptr(), ctypes.c_float(8.0), 1, 64, 543, 2, 6, None,
+        outs[0][0].data_ptr(), outs[0][1].data_ptr(), outs[0][2].data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc < 0 and b"at most 544" in lib.ink_last_error()
