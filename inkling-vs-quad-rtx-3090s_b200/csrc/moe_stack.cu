@@ -61,6 +61,7 @@ enum TraceSlot {
   kTrXDigits = 11, kTrXVisible = 15,                                         // tensor-core variant, consumers
   kTrMmaGuStart = 16, kTrMmaGuEnd = 17, kTrMmaDownStart = 18, kTrMmaDownEnd = 19,   // the issuing thread
   kTrScalesGuEnd = 20, kTrScalesDownEnd = 21,                                // first warp that writes weight scales
+  kTrRowsSent = 22, kTrNormReduced = 23,                                     // the warp that hands the block's rows over; consumers
 };
 __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
@@ -121,8 +122,7 @@ struct StackArgs {
   uint16_t* residual;              // [2][hidden] BF16: slot 0 holds the incoming residual stream (glue mode)
   uint16_t* normed_out;            // [hidden] BF16 output of the last norm (glue mode)
   float* partial;                  // [hidden] FP32 output of the (last) block
-  unsigned long long* logits;      // scratch [2][experts + n_shared] tagged words {BF16-rounded logit, tag}
-  unsigned long long* scores;      // scratch [2][experts] tagged words {selection score, tag}
+  unsigned long long* scores;      // scratch [2][experts + n_shared] router words {selection score, BF16 logit, 16-bit tag}
   uint16_t* activated;             // scratch [2][top_k][f]
   uint16_t* shared_activated;      // scratch [2][n_shared][f]
   RouteTable* routes;              // scratch [n_layers]
@@ -139,6 +139,8 @@ struct StackArgs {
   unsigned long long* peer_inbox[kSMaxWorld];   // the same region of every rank, as mapped into this process
   unsigned long long* summed;      // scratch [2][hidden] tagged words: the rows summed over the ranks, for every block of this rank
   long long wait_limit;            // SM clocks a wait may take before the launch gives up
+  unsigned poll_pause_ns;          // pause between two polls of a hand-over word
+  int prefetch_laps;               // laps of the ring a tile is requested from the L2 ahead of its copy (0: no prefetch)
   int32_t* status;
   unsigned long long* trace;       // optional [n_layers][kTraceBlocks][kTraceSlots] nanosecond stamps
 };
@@ -167,14 +169,17 @@ struct StackShape {
   static constexpr int RPP = 32 / LPR;
   static constexpr int RT = F >= 2048 ? 4 : 8192 / F;
   static constexpr int PASSES = RT / RPP;
-  static constexpr int QD_CODES = RT * (F / 2);
-  static constexpr int QD_SCALES = RT * (F / 16);
+  static constexpr int QD_CODES = RT * (F / 2);             // one row group: 4096 bytes of codes ...
+  static constexpr int QD_SCALES = RT * (F / 16);           // ... and 512 of scales
+  // a routed down tile of the CUDA-core path holds up to QD_PAIR consecutive row groups (codes of all of them, then
+  // their scales): one producer lane issues about two tiles per microsecond, so tiles have to be this large
+  static constexpr int QD_PAIR = 2;
   static constexpr int SD_ROWS = 8192 / (F * 2) < RT ? 8192 / (F * 2) : RT;   // BF16 rows per tile
   static constexpr int SD_PER_GROUP = RT / SD_ROWS;
   static constexpr int SD_BYTES = SD_ROWS * F * 2;
   static constexpr int SD_CPL = F / 256;
   static_assert(R_BYTES <= kSSlot && 2 * SG_PART <= kSSlot && QG_CODES + QG_SCALES <= kSSlot, "tile exceeds slot");
-  static_assert(QD_CODES + QD_SCALES <= kSSlot && SD_BYTES <= kSSlot, "tile exceeds slot");
+  static_assert(QD_PAIR * (QD_CODES + QD_SCALES) <= kSSlot && SD_BYTES <= kSSlot, "tile exceeds slot");
   // staging that overlays: [x FP16 | x BF16] during gate/up, [routed act FP16 | shared act BF16] during down
   // tensor-core path: [x digit rows D*4 | x BF16] during gate/up
   static constexpr int GU_TILES = 2 * F / kTcRows;          // 128-row tiles per expert
@@ -204,6 +209,7 @@ struct TilePlan {
   int qu0, n_qu;          // tensor-core path: routed gate/up units [qu0, qu0 + n_qu) of top_k * GU_TILES * GU_CHUNKS
   int du0, n_du;          // and routed down units of top_k * DN_TILES * DN_CHUNKS
   int n_sd_real;          // shared down tiles without the padding tile that keeps the units on even slots
+  int n_gt;               // routed down tiles per route on the CUDA-core path (QD_PAIR row groups each, the last maybe fewer)
 };
 
 template <int D, int F>
@@ -230,7 +236,8 @@ __device__ __forceinline__ TilePlan make_plan(const StackArgs& a, bool tc) {
   const int pad_r = (p.n_r + kSC - 1) / kSC * kSC;
   p.n_sg = (p.n_u + kSC - 1) / kSC * kSC * S::SG_SPLIT;
   p.n_sd = p.n_sd_real = a.n_shared * p.n_g * S::SD_PER_GROUP;
-  p.n_qd = a.top_k * p.n_g;
+  p.n_gt = (p.n_g + S::QD_PAIR - 1) / S::QD_PAIR;
+  p.n_qd = a.top_k * p.n_gt;
   const long long dn_units = (long long)a.top_k * S::DN_TILES * S::DN_CHUNKS;
   p.du0 = (int)(b * dn_units / G);
   p.n_du = (int)((b + 1) * dn_units / G) - p.du0;
@@ -248,24 +255,39 @@ __device__ __forceinline__ TilePlan make_plan(const StackArgs& a, bool tc) {
   return p;
 }
 
+// What the routing of a layer needs besides the scores, brought into shared memory by the auxiliary warp
+// while the previous layer is still streaming: under a saturated memory system a dependent global load
+// takes microseconds, and the routing has four of them in a row on the layer's critical path.
+struct RouteConsts {
+  const uint8_t* bank[kSMaxExperts][4];   // gate/up codes, gate/up scales, down codes, down scales (null: not on this rank)
+  float gu_scale2[kSMaxExperts];
+  float dn_scale2[kSMaxExperts];
+  float bias[kSMaxExperts];
+  float global_scale, route_scale;
+};
+
 struct StackShared {
   uint64_t full[kSStages];
   uint64_t empty[kSStages];
   RouteTable routes[2];                 // by layer parity; filled by the producer warp
   float contrib[kSMaxTopK + kSMaxShared][kSMaxRows];
-  float score[kSMaxExperts];            // auxiliary warp scratch
+  float logit[kSMaxExperts + kSMaxShared];   // auxiliary warp scratch: the layer's BF16-rounded logits (routed rows, then shared rows)
   float red[kSC][4];                    // consumer reductions
   float inverse[kSMaxTopK];             // inverse normalisers of the staged routed activations
   float x_inverse;                      // inverse normaliser of the staged x
   int done[2][3];                       // tiles finished per layer parity: shared g/u, routed g/u, down
   unsigned epoch1;                      // launches completed before this one, plus one: scales every target
   long long limit;                      // SM clocks a wait may take
+  unsigned pause;                       // nanoseconds between two polls of a word that other blocks write
+  volatile int rows_seen;               // layers whose summed output rows consumer warp 0 has seen arrive
   volatile int routed_layers;           // layers whose routing table is in `routes` (set by the auxiliary warp)
   volatile int seen[2];                 // layers whose grid-wide counters (shared gate/up, routed gate/up) the auxiliary
                                         // warp has seen complete: one poller per block instead of one per warp
   volatile int sact_flag[kSMaxShared];  // layers whose shared-expert activations are staged, per shared expert
   volatile int act_flag[kSMaxTopK];     // layers whose routed activations are staged, per route
   volatile int failed;
+  volatile int consts_layers;           // layers whose routing constants have been loaded into `consts` (set by the auxiliary warp)
+  RouteConsts consts;
   // tensor-core path
   uint64_t sf_full[kTcSfSlots], sf_empty[kTcSfSlots];   // weight scales of a unit are in tensor memory / may be overwritten
   uint64_t d_full[2], d_empty[2];                        // accumulator of a tile segment is complete / has been read
@@ -318,7 +340,7 @@ __device__ __forceinline__ bool wait_global(const unsigned* p, unsigned target, 
       sh->failed = 1;
       return false;
     }
-    __nanosleep(32);
+    __nanosleep(sh->pause);   // a counter is polled by every block: polling it harder only delays the increments
   }
   return true;
 }
@@ -351,6 +373,14 @@ __device__ __forceinline__ float value_of(unsigned long long word) { return __ui
 // The tag of a layer of a launch. Never zero before the epoch wraps, so a zero-filled buffer matches nothing.
 __device__ __forceinline__ unsigned layer_tag(unsigned epoch1, int n_layers, int layer) {
   return epoch1 * (unsigned)n_layers + (unsigned)layer;
+}
+// A router row's word: {FP32 selection score, BF16 logit, 16-bit tag} -- score and logit arrive together, so the
+// routing needs one poll and no second round trip. The 16-bit tag is never zero and repeats only after 65 535
+// layers, long after the word has been overwritten (the two sets of words alternate from layer to layer).
+__device__ __forceinline__ unsigned router_tag(unsigned tag) { return tag % 65535u + 1u; }
+__device__ __forceinline__ unsigned long long router_word(float score, float logit_bf16, unsigned tag16) {
+  return (unsigned long long)__float_as_uint(score) | ((unsigned long long)(__float_as_uint(logit_bf16) >> 16) << 32) |
+         ((unsigned long long)tag16 << 48);
 }
 // Bounded wait for one tagged word; the value, or 0 once the launch has failed.
 __device__ __forceinline__ float wait_tagged(const unsigned long long* p, unsigned tag, StackShared* sh) {
@@ -402,59 +432,111 @@ __device__ __forceinline__ void consumer_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(kSC * 32) : "memory");
 }
 
-// -------------------------------------------------------------------- router tail
-// One warp. Waits for the layer's scores as the blocks publish them (tagged words), then
-// resolves the routing. Returns false if the launch failed while waiting.
-__device__ bool stack_router_tail(const StackArgs& a, const StackLayer& ly, int layer, StackShared* sh) {
+// One warp: the routing constants of `layer` from global into shared memory (all loads of a pass in flight together).
+__device__ void load_route_consts(const StackArgs& a, int layer, StackShared* sh) {
   const int lane = threadIdx.x & 31;
-  const int par = layer & 1;
-  const unsigned tag = layer_tag(sh->epoch1, a.n_layers, layer);
-  const unsigned long long* logit = a.logits + (size_t)par * (a.experts + a.n_shared);
-  const unsigned long long* scores = a.scores + (size_t)par * a.experts;
-  float* score = sh->score;
-  {
-    // all of the lane's words in one round trip, then only the missing ones again
-    constexpr int kPerLane = kSMaxExperts / 32;
-    unsigned missing = 0;
+  const StackLayer* ly = a.layers + layer;
+  const int64_t* sources = ly->sources;
+  const float* bias = ly->router_bias;
+  RouteConsts& c = sh->consts;
+  if (lane == 0) {
+    c.global_scale = bf16_to_f32(ly->global_scale[0]);
+    c.route_scale = ly->route_scale;
+  }
+#pragma unroll 1
+  for (int e0 = 0; e0 < a.experts; e0 += 128) {
+    longlong2 row[4][3];
 #pragma unroll
-    for (int i = 0; i < kPerLane; ++i) {
-      const int e = i * 32 + lane;
+    for (int i = 0; i < 4; ++i) {
+      const int e = e0 + i * 32 + lane;
+#pragma unroll
+      for (int k = 0; k < 3; ++k)
+        row[i][k] = e < a.experts ? __ldg(reinterpret_cast<const longlong2*>(sources + (size_t)e * kBank) + k) : make_longlong2(0, 0);
+    }
+    float s2[4][2], b[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int e = e0 + i * 32 + lane;
+      // entries: 0 codes, 1 scales, 2 scale2 | 3 codes, 4 scales, 5 scale2
+      s2[i][0] = row[i][0].x ? __ldg(reinterpret_cast<const float*>(row[i][1].x)) : 0.f;
+      s2[i][1] = row[i][1].y ? __ldg(reinterpret_cast<const float*>(row[i][2].y)) : 0.f;
+      b[i] = e < a.experts ? __ldg(bias + e) : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int e = e0 + i * 32 + lane;
       if (e < a.experts) {
-        const unsigned long long w = ld_tagged(scores + e);
-        if (has_tag(w, tag)) score[e] = value_of(w);
-        else missing |= 1u << i;
+        c.bank[e][0] = reinterpret_cast<const uint8_t*>(row[i][0].x);
+        c.bank[e][1] = reinterpret_cast<const uint8_t*>(row[i][0].y);
+        c.bank[e][2] = reinterpret_cast<const uint8_t*>(row[i][1].y);
+        c.bank[e][3] = reinterpret_cast<const uint8_t*>(row[i][2].x);
+        c.gu_scale2[e] = s2[i][0];
+        c.dn_scale2[e] = s2[i][1];
+        c.bias[e] = b[i];
       }
     }
-    const long long t0 = clock64();
-    while (__any_sync(0xffffffffu, missing != 0) && !sh->failed) {
-      __nanosleep(64);
-#pragma unroll
-      for (int i = 0; i < kPerLane; ++i) {
-        if ((missing >> i) & 1u) {
-          const int e = i * 32 + lane;
-          const unsigned long long w = ld_tagged(scores + e);
-          if (has_tag(w, tag)) {
-            score[e] = value_of(w);
-            missing &= ~(1u << i);
-          }
-        }
-      }
-      if (clock64() - t0 > sh->limit) sh->failed = 1;
-    }
-    if (sh->failed) return false;
   }
   __syncwarp();
+  if (lane == 0) {
+    __threadfence_block();
+    sh->consts_layers = layer + 1;
+  }
+}
+
+// -------------------------------------------------------------------- router tail
+// One warp: the layer's router words as the blocks publish them. Lane l ends up with the selection scores
+// of the experts l, l + 32, ... in registers (`sc`, -inf beyond the routed experts) and every row's logit in
+// shared memory. One round of loads at a time, only the words still missing, with a pause between rounds:
+// every block polls the same few lines, and on B200 polling them harder (two rounds in flight, no pause) made
+// the words arrive later, not sooner -- the loads queue up in front of the stores. False: the launch failed.
+template <int K>
+__device__ __forceinline__ bool poll_router_words(const StackArgs& a, const unsigned long long* words, unsigned tag16, int rows,
+                                                  float (&sc)[K], StackShared* sh) {
+  const int lane = threadIdx.x & 31;
+  float* logit = sh->logit;
+  const unsigned long long found = (unsigned long long)tag16 << 48;   // stands for a row this lane does not have
+#pragma unroll
+  for (int i = 0; i < K; ++i) sc[i] = -INFINITY;
+  unsigned long long w[K];
+  unsigned missing = 0;
+#pragma unroll
+  for (int i = 0; i < K; ++i)
+    if (i * 32 + lane < rows) missing |= 1u << i;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll
+    for (int i = 0; i < K; ++i) w[i] = (missing >> i) & 1u ? ld_tagged(words + i * 32 + lane) : found;
+#pragma unroll
+    for (int i = 0; i < K; ++i) {
+      const int e = i * 32 + lane;
+      if (((missing >> i) & 1u) && (unsigned)(w[i] >> 48) == tag16) {
+        if (e < a.experts) sc[i] = __uint_as_float((unsigned)w[i]);
+        logit[e] = __uint_as_float((unsigned)(w[i] >> 32) << 16);
+        missing &= ~(1u << i);
+      }
+    }
+    if (__all_sync(0xffffffffu, missing == 0)) break;
+    if (sh->failed) return false;
+    if (clock64() - t0 > sh->limit) sh->failed = 1;
+    __nanosleep(sh->pause);
+  }
+  return !sh->failed;
+}
+
+// The top_k largest scores over the lanes' registers (ties: the lower expert id); lane r returns choice r.
+template <int K>
+__device__ __forceinline__ int select_top_k(float (&sc)[K], int top_k) {
+  const int lane = threadIdx.x & 31;
   int my_choice = 0;
 #pragma unroll 1
-  for (int r = 0; r < a.top_k; ++r) {
+  for (int r = 0; r < top_k; ++r) {
     float best = -INFINITY;
     int best_e = 0x7fffffff;
-#pragma unroll 1
-    for (int e = lane; e < a.experts; e += 32) {
-      const float v = score[e];
-      if (v > best) {
-        best = v;
-        best_e = e;
+#pragma unroll
+    for (int i = 0; i < K; ++i) {
+      if (sc[i] > best) {
+        best = sc[i];
+        best_e = i * 32 + lane;
       }
     }
 #pragma unroll
@@ -467,15 +549,42 @@ __device__ bool stack_router_tail(const StackArgs& a, const StackLayer& ly, int 
       }
     }
     if (best_e == 0x7fffffff) best_e = r;
-    if (lane == 0) score[best_e] = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < K; ++i)
+      if (i * 32 + lane == best_e) sc[i] = -INFINITY;
     if (lane == r) my_choice = best_e;
-    __syncwarp();
   }
+  return my_choice;
+}
+
+// One warp. Waits for the layer's scores as the blocks publish them (router words), then
+// resolves the routing. Returns false if the launch failed while waiting.
+__device__ bool stack_router_tail(const StackArgs& a, const StackLayer& ly, int layer, StackShared* sh) {
+  const int lane = threadIdx.x & 31;
+  const int par = layer & 1;
+  const unsigned tag16 = router_tag(layer_tag(sh->epoch1, a.n_layers, layer));
+  const int rows = a.experts + a.n_shared;
+  const unsigned long long* words = a.scores + (size_t)par * rows;
+  const float* logit = sh->logit;
+  int my_choice;
+  constexpr int kFew = 9, kMany = (kSMaxExperts + kSMaxShared + 31) / 32;   // router rows per lane: up to 288, up to 514
+  if (rows <= kFew * 32) {
+    float sc[kFew];
+    if (!poll_router_words<kFew>(a, words, tag16, rows, sc, sh)) return false;
+    if (lane == 0) INK_TRACE(layer, kTrXDigits);   // (CUDA-core variant: all scores of the layer have arrived)
+    my_choice = select_top_k<kFew>(sc, a.top_k);
+  } else {
+    float sc[kMany];
+    if (!poll_router_words<kMany>(a, words, tag16, rows, sc, sh)) return false;
+    if (lane == 0) INK_TRACE(layer, kTrXDigits);
+    my_choice = select_top_k<kMany>(sc, a.top_k);
+  }
+  __syncwarp();
   const int n = a.top_k + a.n_shared;
   const bool live = lane < n;
   float l = 0.f;
-  if (lane < a.top_k) l = wait_tagged(logit + my_choice, tag, sh);
-  else if (live) l = wait_tagged(logit + a.experts + (lane - a.top_k), tag, sh);
+  if (lane < a.top_k) l = logit[my_choice];
+  else if (live) l = logit[a.experts + (lane - a.top_k)];
   const float lp = live ? round_bf16(fminf(0.f, l) - log1pf(__expf(-fabsf(l)))) : -INFINITY;
   float m = lp;
 #pragma unroll
@@ -487,32 +596,37 @@ __device__ bool stack_router_tail(const StackArgs& a, const StackLayer& ly, int 
   for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
   const float lse = round_bf16(round_bf16(__logf(round_bf16(s))) + m);
   float w = round_bf16(__expf(round_bf16(lp - lse)));
-  w = round_bf16(w * ly.route_scale);
-  w = round_bf16(w * bf16_to_f32(ly.global_scale[0]));
+  const RouteConsts& c = sh->consts;    // loaded for this layer before the scores could be complete (see the caller)
+  w = round_bf16(w * c.route_scale);
+  w = round_bf16(w * c.global_scale);
   RouteTable* table = &sh->routes[layer & 1];
-  const bool publish = blockIdx.x == 0;   // one block also writes the optional router outputs
   if (lane < a.top_k) {
-    const int64_t* entry = ly.sources + (size_t)my_choice * kBank;
     RouteEntry r;
-    r.gu_codes = reinterpret_cast<const uint8_t*>(entry[0]);
-    r.gu_scales = reinterpret_cast<const uint8_t*>(entry[1]);
-    r.gu_scale2 = r.gu_codes ? *reinterpret_cast<const float*>(entry[2]) : 0.f;
-    r.dn_codes = reinterpret_cast<const uint8_t*>(entry[3]);
-    r.dn_scales = reinterpret_cast<const uint8_t*>(entry[4]);
-    r.dn_scale2 = r.dn_codes ? *reinterpret_cast<const float*>(entry[5]) : 0.f;
+    r.gu_codes = c.bank[my_choice][0];
+    r.gu_scales = c.bank[my_choice][1];
+    r.gu_scale2 = c.gu_scale2[my_choice];
+    r.dn_codes = c.bank[my_choice][2];
+    r.dn_scales = c.bank[my_choice][3];
+    r.dn_scale2 = c.dn_scale2[my_choice];
     r.weight = w;
     r.expert = my_choice;
     table->route[lane] = r;
-    if (publish && ly.topk_indices) ly.topk_indices[lane] = my_choice;
-    if (publish && ly.topk_weights) ly.topk_weights[lane] = (uint16_t)f32_to_bf16_bits(w);
   } else if (live) {
     table->gamma[lane - a.top_k] = w;
-    if (publish && ly.gammas) ly.gammas[lane - a.top_k] = (uint16_t)f32_to_bf16_bits(w);
   }
   __syncwarp();
   if (lane == 0) {
     __threadfence_block();
     sh->routed_layers = layer + 1;   // the producer and the consumers of this block may read the table
+    INK_TRACE(layer, kTrXVisible);   // (CUDA-core variant: the routing is resolved)
+  }
+  if (blockIdx.x == 0) {   // one block also writes the optional router outputs (off the critical path)
+    if (lane < a.top_k) {
+      if (ly.topk_indices) ly.topk_indices[lane] = my_choice;
+      if (ly.topk_weights) ly.topk_weights[lane] = (uint16_t)f32_to_bf16_bits(w);
+    } else if (live && ly.gammas) {
+      ly.gammas[lane - a.top_k] = (uint16_t)f32_to_bf16_bits(w);
+    }
   }
   return true;
 }
@@ -772,12 +886,15 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
     sh.sg_done = 0;
     sh.issued = 0;
     sh.routed_layers = 0;
+    sh.consts_layers = 0;
     for (int i = 0; i < 2; ++i) sh.seen[i] = 0;
     for (int i = 0; i < kSMaxShared; ++i) sh.sact_flag[i] = 0;
     for (int i = 0; i < kSMaxTopK; ++i) sh.act_flag[i] = 0;
     sh.failed = 0;
     sh.epoch1 = *a.epoch + 1u;
     sh.limit = a.wait_limit;
+    sh.pause = a.poll_pause_ns;
+    sh.rows_seen = 0;
     for (int i = 0; i < 6; ++i) (&sh.done[0][0])[i] = 0;
     mbar_init_fence();
   }
@@ -810,10 +927,142 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
   __syncthreads();
   const uint32_t tmem = tc ? sh.tmem_base : 0u;
 
-  if (warp == 0) {
-    // =========================================================== producer (one lane)
-    // The tile list is walked with running counters: a division per tile on a single
-    // thread would cost more than issuing the copy.
+  if (warp == 0 && !tc) {
+    // =========================================================== producer (one lane per ring slot)
+    // A single thread issues about two tiles per microsecond (a wait on the slot's barrier, the
+    // transaction count, two bulk copies: each a long-latency instruction), which caps one block at
+    // ~18 KB/us, a third of its share of the HBM bandwidth. So lane s of this warp owns ring slot s
+    // and issues the tiles s, s + 16, ... of the block's whole sequence on its own; the tile's place
+    // in the layer is worked out from its index (the divisions run on sixteen lanes at once).
+    if (lane < kSStages) {
+      constexpr int kQgPerJob = 2 * F / S::QG_ROWS;
+      const int kAhead = a.prefetch_laps * kSStages;   // tiles between a tile's prefetch into L2 and its copy into the ring
+      const long long n_total = (long long)a.n_layers * plan.per_layer;
+      unsigned char* dst = slots + (size_t)lane * kSSlot;
+      uint64_t* bar = &sh.full[lane];
+      // the weight pointers of two layers (this one and the one the prefetches have reached), by layer parity
+      struct LayerPointers { const uint16_t *router_weight, *shared_gate, *shared_up, *shared_down; int layer; } even, odd;
+      even.layer = odd.layer = -1;
+      auto pointers_of = [&](int layer) -> const LayerPointers& {
+        LayerPointers& h = (layer & 1) ? odd : even;
+        if (h.layer != layer) {
+          const StackLayer* ly = a.layers + layer;
+          h.router_weight = ly->router_weight;
+          h.shared_gate = ly->shared_gate;
+          h.shared_up = ly->shared_up;
+          h.shared_down = ly->shared_down;
+          h.layer = layer;
+        }
+        return h;
+      };
+      // One or two contiguous pieces of global memory that make up tile t of a layer; `second_at` is where the
+      // second piece goes in the slot. A routed tile can only be described once its layer's routing is known.
+      struct Tile { const void *first, *second; uint32_t first_bytes, second_bytes, second_at; };
+      auto describe = [&](int layer, int t, Tile& d) -> bool {
+        d.first = d.second = nullptr;
+        d.first_bytes = d.second_bytes = d.second_at = 0;
+        if (t < plan.s_sg) {
+          // ---- router rows, padded to a multiple of the consumer count
+          if (t < plan.n_r) {
+            d.first = pointers_of(layer).router_weight + (size_t)(plan.r0 + t) * D;
+            d.first_bytes = S::R_BYTES;
+          }
+        } else if (t < plan.s_qg) {
+          // ---- shared gate/up: blocks of kSC units, each unit SG_SPLIT column slabs
+          const int k = t - plan.s_sg;
+          const int h = (k / kSC) % S::SG_SPLIT, unit = k / (kSC * S::SG_SPLIT) * kSC + k % kSC;
+          if (unit < plan.n_u) {
+            const size_t off = (size_t)(plan.u0 + unit) * S::SG_PAIRS * D + (size_t)h * S::SG_COLS;
+            const LayerPointers& lp = pointers_of(layer);
+            d.first = lp.shared_gate + off;
+            d.second = lp.shared_up + off;
+            d.first_bytes = d.second_bytes = d.second_at = S::SG_PART;
+          }
+        } else if (t < plan.s_sd) {
+          // ---- routed gate/up
+          if (sh.routed_layers <= layer) return false;
+          __threadfence_block();
+          const int q = plan.q0 + (t - plan.s_qg);
+          const int choice = q / kQgPerJob, row0 = (q % kQgPerJob) * S::QG_ROWS;
+          const RouteEntry& r = sh.routes[layer & 1].route[choice];
+          if (r.gu_codes) {
+            d.first = r.gu_codes + (size_t)row0 * (D / 2);
+            d.second = r.gu_scales + (size_t)row0 * (D / 16);
+            d.first_bytes = d.second_at = S::QG_CODES;
+            d.second_bytes = S::QG_SCALES;
+          }
+        } else if (t < plan.s_qd) {
+          // ---- shared down: expert-major, then row group, then the tiles of a group
+          const int k = t - plan.s_sd, per_e = plan.n_g * S::SD_PER_GROUP;
+          const int e = k / per_e, rem = k % per_e;
+          d.first = pointers_of(layer).shared_down + ((size_t)e * D + (size_t)plan.g0 * S::RT) * F + (size_t)rem * S::SD_ROWS * F;
+          d.first_bytes = S::SD_BYTES;
+        } else if (t < plan.s_pad) {
+          // ---- routed down: choice-major, then pairs of row groups
+          if (sh.routed_layers <= layer) return false;
+          __threadfence_block();
+          const int k = t - plan.s_qd;
+          const int choice = k / plan.n_gt, first = (k % plan.n_gt) * S::QD_PAIR;
+          const uint32_t groups = (uint32_t)min(S::QD_PAIR, plan.n_g - first);
+          const RouteEntry& r = sh.routes[layer & 1].route[choice];
+          if (r.dn_codes) {
+            const size_t row0 = (size_t)(plan.g0 + first) * S::RT;
+            d.first = r.dn_codes + row0 * (F / 2);
+            d.second = r.dn_scales + row0 * (F / 16);
+            d.first_bytes = groups * S::QD_CODES;
+            d.second_bytes = groups * S::QD_SCALES;
+            d.second_at = S::QD_PAIR * S::QD_CODES;
+          }
+        }   // else: padding up to a multiple of the consumer count
+        return true;
+      };
+      int layer = 0, t = lane;                 // the tile to copy
+      int ahead_layer = 0, ahead_t = lane;     // the tile to prefetch, kAhead further on
+      for (int k = 0; k < kAhead / kSStages; ++k) {   // the first tiles are copied without having been prefetched
+        ahead_t += kSStages;
+        while (ahead_t >= plan.per_layer) {
+          ahead_t -= plan.per_layer;
+          ++ahead_layer;
+        }
+      }
+      for (long long i = lane; i < n_total; i += kSStages, t += kSStages, ahead_t += kSStages) {
+        while (t >= plan.per_layer) {
+          t -= plan.per_layer;
+          ++layer;
+        }
+        while (ahead_t >= plan.per_layer) {
+          ahead_t -= plan.per_layer;
+          ++ahead_layer;
+        }
+        if (sh.failed) break;
+        Tile d;
+        // Ask the L2 for the tile two laps of the ring ahead: the copy into the ring then finds it there, so
+        // the bytes in flight to HBM are no longer bounded by the ring (eight slots of it are in use by the
+        // consumers at any time), and the stream goes on while the consumers stand at a grid-wide hand-over.
+        if (kAhead > 0 && ahead_layer < a.n_layers && describe(ahead_layer, ahead_t, d)) {
+          if (d.first_bytes) bulk_prefetch_l2(d.first, d.first_bytes);
+          if (d.second_bytes) bulk_prefetch_l2(d.second, d.second_bytes);
+        }
+        if (t == plan.s_qg) INK_TRACE(layer, kTrProdRouteWait);
+        if ((t >= plan.s_qg && t < plan.s_sd) || (t >= plan.s_qd && t < plan.s_pad)) {
+          if (!wait_routing(layer, &sh)) break;
+        }
+        if (t == plan.s_qg) INK_TRACE(layer, kTrProdRouteGot);
+        describe(layer, t, d);
+        if (i >= kSStages && !mbar_wait(&sh.empty[lane], (uint32_t)((i / kSStages) - 1) & 1, sh.limit)) {
+          sh.failed = 1;
+          break;
+        }
+        mbar_expect_tx(bar, d.first_bytes + d.second_bytes);
+        if (d.first_bytes) bulk_g2s(dst, d.first, d.first_bytes, bar);
+        if (d.second_bytes) bulk_g2s(dst + d.second_at, d.second, d.second_bytes, bar);
+        if (t == plan.s_pad - 1) INK_TRACE(layer, kTrProdLayerIssued);
+      }
+    }
+  } else if (warp == 0) {
+    // =========================================================== producer (one lane, tensor-core variant)
+    // The tile list is walked in order with running counters; the tensor-core warps rely on that order
+    // (see tc_wait_issued).
     if (lane == 0) {
       long long issued = 0;   // tiles issued so far (all layers)
       bool alive = true;
@@ -990,11 +1239,15 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
   } else if (warp == kSC + 1) {
     // =========================================================== auxiliary warp
     long long tc_base = 0, qseq = 0, dseq = 0;   // ring index of the layer's first tile; units and tile segments so far
+    load_route_consts(a, 0, &sh);
     for (int layer = 0; layer < a.n_layers; ++layer) {
       const unsigned* sync = a.sync + (size_t)layer * kSyncWordsPerLayer;
       // every block resolves the routing for itself (same inputs, same arithmetic, same result): the
       // code stays warm in this SM's instruction cache and nothing has to be published between blocks
       if (!stack_router_tail(a, a.layers[layer], layer, &sh)) break;
+      // the constants of this layer are in the route table now; fetch the next layer's while this one streams.
+      // (The consumers read this layer's biases only before they publish its scores, i.e. before this point.)
+      if (layer + 1 < a.n_layers) load_route_consts(a, layer + 1, &sh);
       if (!tc && lane == 0) {
         // One lane polls the layer's grid-wide counters for the whole block and raises a flag in shared memory
         // for each: eight polling warps per block crowd the counter's L2 line and hold up its increments.
@@ -1144,7 +1397,6 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
     }
 
     for (int layer = 0; layer < a.n_layers; ++layer, base += plan.per_layer) {
-      const float* router_bias = a.layers[layer].router_bias;
       const uint16_t* norm_weight = a.layers[layer].norm_weight;
       unsigned* sync = a.sync + (size_t)layer * kSyncWordsPerLayer;
       const int par = layer & 1;
@@ -1161,6 +1413,7 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
         if (plan.n_q == 0 && !tc) red_release_add(sync + kRtGuDone, 1u);   // (the tensor-core path counts tiles)
       }
       // ------------------------------------------------ router rows
+      if (plan.n_r > 0) wait_flag(&sh.consts_layers, layer, &sh, lane);   // the layer's biases (loaded a layer ahead)
       for (int t = first_of(plan.s_r); t < plan.s_sg; t += kSC) {
         const unsigned char* src;
         int slot;
@@ -1175,11 +1428,11 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
           acc = warp_sum(acc);
           release(slot);
           const int row = plan.r0 + t;
-          if (lane == 0) {   // tagged words: the routing warps of all blocks poll for them
+          if (lane == 0) {   // one word per row: the routing warps of all blocks poll for them
             const float l = round_bf16(acc);
-            st_tagged(a.logits + (size_t)par * total_rows + row, l, tag);
-            if (row < a.experts)
-              st_tagged(a.scores + (size_t)par * a.experts + row, round_bf16(1.f / (1.f + __expf(-l))) + router_bias[row], tag);
+            const float score = row < a.experts ? round_bf16(1.f / (1.f + __expf(-l))) + sh.consts.bias[row] : 0.f;
+            unsigned long long* at = a.scores + (size_t)par * total_rows + row;
+            asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(at), "l"(router_word(score, l, router_tag(tag))) : "memory");
           }
         } else {
           release(slot);
@@ -1383,6 +1636,7 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
             if (__shfl_sync(0xffffffffu, last, 0)) {
               __threadfence();
               finish_row_tile<D, F>(a, &sh, layer, par, xpar, tile, lane, 32);
+              __syncwarp();   // (the lanes waited for different rows)
             }
           }
         }
@@ -1414,7 +1668,8 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
           int slot;
           if (!take(t, src, slot)) break;
           const int i = t - plan.s_qd;
-          const int choice = i / plan.n_g, local0 = (i % plan.n_g) * S::RT;
+          const int choice = i / plan.n_gt, first_group = (i % plan.n_gt) * S::QD_PAIR;
+          const int groups_here = min(S::QD_PAIR, plan.n_g - first_group);
           const RouteEntry r = sh.routes[par].route[choice];
           if (r.dn_codes) {
             if (loaded != choice) {
@@ -1431,6 +1686,12 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
               }
             }
             const float scale = r.dn_scale2 * sh.inverse[choice];
+            const unsigned char* tile = src;
+#pragma unroll 1
+            for (int sub = 0; sub < groups_here; ++sub) {
+            const int local0 = (first_group + sub) * S::RT;
+            const unsigned char* src = tile + (size_t)sub * S::QD_CODES;                                  // this group's codes
+            const unsigned char* src_scales = tile + S::QD_PAIR * S::QD_CODES + (size_t)sub * S::QD_SCALES;   // and scales
             if constexpr (S::LPR == 32) {
               // a row spans the warp: every lane accumulates its columns of all RT rows, one multi-row reduction
               float acc[S::RT];
@@ -1441,7 +1702,7 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
                 for (int j = 0; j < S::QD_CPL; ++j) {
                   const int chunk = j * 32 + lane;
                   sum += dot32(*reinterpret_cast<const uint4*>(src + (size_t)row * (F / 2) + chunk * 16),
-                               *reinterpret_cast<const uint16_t*>(src + S::QD_CODES + (size_t)row * (F / 16) + chunk * 2), xr[j]);
+                               *reinterpret_cast<const uint16_t*>(src_scales + (size_t)row * (F / 16) + chunk * 2), xr[j]);
                 }
                 acc[row] = sum;
               }
@@ -1459,7 +1720,7 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
                 for (int j = 0; j < S::QD_CPL; ++j) {
                   const int chunk = j * S::LPR + sl;
                   acc += dot32(*reinterpret_cast<const uint4*>(src + (size_t)row * (F / 2) + chunk * 16),
-                               *reinterpret_cast<const uint16_t*>(src + S::QD_CODES + (size_t)row * (F / 16) + chunk * 2), xr[j]);
+                               *reinterpret_cast<const uint16_t*>(src_scales + (size_t)row * (F / 16) + chunk * 2), xr[j]);
                 }
 #pragma unroll
                 for (int o = S::LPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -1469,6 +1730,7 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
                 }
               }
             }
+            }   // row groups of the tile
             release(slot);
           } else {
             release(slot);
@@ -1487,8 +1749,10 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
             for (int j = 0; j < n_jobs; ++j) total += sh.contrib[j][row];
             send_row<D>(a, xpar, tag, plan.g0 * S::RT + row, total);
           }
+          if (lane == 0) INK_TRACE(layer, kTrRowsSent);
           if (a.world > 1)
             for (int row = lane; row < plan.n_g * S::RT; row += 32) gather_row<D>(a, &sh, xpar, tag, plan.g0 * S::RT + row);
+          __syncwarp();   // the lanes waited for different rows: together again before anything warp-wide
         }
       }
       }   // CUDA-core routed down
@@ -1519,7 +1783,10 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
         float sumsq = 0.f, amax_h = 0.f, amax_w = 0.f;
         // all loads first (they are independent), arithmetic after: one L2 round trip; 16-byte loads of eight
         // consecutive elements keep both the loads and the code that follows short
-        const bool live = !sh.failed && holder;
+        // (one answer per warp: what follows synchronises the warp, so its lanes must not disagree about a
+        // failure that another warp reports while they read the flag)
+        __syncwarp();
+        const bool live = !__any_sync(0xffffffffu, sh.failed != 0) && holder;
         uint4 res[VG], nw[VG];
         float part[VG][8];
 #pragma unroll
@@ -1535,6 +1802,32 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
         // the last row it needs is there -- no counter, no fence.
         if (live) {
           unsigned long long w[VG][8];
+          // Polling has to be gentle: every block polls the same 32 KB, and on B200 the polls delay the very stores
+          // they wait for (a round of everything from every thread costs the L2 more than the rows take to arrive).
+          // So ONE warp of the block watches one word per sending block -- the last row of its slice -- with a pause
+          // between rounds, and raises a flag for the other warps ...
+          if (cw == 0) {
+            const int groups = D / S::RT;
+            const long long t0 = clock64();
+            for (;;) {
+              bool there = true;
+              for (int b = lane; b < (int)gridDim.x; b += 32) {
+                const int first = (int)((long long)b * groups / gridDim.x), end = (int)((long long)(b + 1) * groups / gridDim.x);
+                if (end > first) there = there && has_tag(ld_tagged(summed + (size_t)end * S::RT - 1), tag);
+              }
+              if (__all_sync(0xffffffffu, there) || sh.failed) break;
+              if (clock64() - t0 > sh.limit) sh.failed = 1;
+              __nanosleep(sh.pause);
+            }
+            __syncwarp();
+            if (lane == 0) {
+              __threadfence_block();
+              sh.rows_seen = layer + 1;
+            }
+          } else {
+            wait_flag(&sh.rows_seen, layer, &sh, lane);
+          }
+          // ... then every thread loads its own elements; a sender's other rows may be a moment behind its last one
           bool all = true;
 #pragma unroll
           for (int g = 0; g < VG; ++g) {
@@ -1550,7 +1843,7 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
           }
           const long long t0 = clock64();
           while (!all && !sh.failed) {
-            __nanosleep(100);
+            __nanosleep(sh.pause);
             all = true;
 #pragma unroll
             for (int g = 0; g < VG; ++g) {
@@ -1612,6 +1905,7 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
           sh.red[cw][2] = amax_w;
         }
         consumer_sync();   // also: every consumer is past its down tiles, staging may be overwritten
+        if (tracer) INK_TRACE(layer, kTrNormReduced);
         sumsq = 0.f;
         amax_h = 0.f;
         amax_w = 0.f;
@@ -2006,8 +2300,7 @@ extern "C" size_t ink_moe_stack_scratch_bytes(int n_layers, int hidden, int inte
   bytes += pad256(sizeof(float) * 2 * (size_t)n_shared * hidden);               // shared experts' down rows
   bytes += pad256(sizeof(unsigned) * 2 * kSMaxTopK);                            // activation maxima
   bytes += pad256(sizeof(unsigned) * kTileCounters * (size_t)n_layers);         // tile counters
-  bytes += pad256(sizeof(unsigned long long) * 2 * (size_t)(experts + n_shared));   // logits (tagged)
-  bytes += pad256(sizeof(unsigned long long) * 2 * (size_t)experts);            // scores (tagged)
+  bytes += pad256(sizeof(unsigned long long) * 2 * (size_t)(experts + n_shared));   // router words
   bytes += pad256(2 * 2 * (size_t)top_k * intermediate);                        // activated
   bytes += pad256(2 * 2 * (size_t)n_shared * intermediate);                     // shared activated
   bytes += pad256(2 * 2 * (size_t)hidden);                                      // residual double buffer
@@ -2066,13 +2359,22 @@ static int stack_decode(const void* layers, int n_layers, const void* x, void* r
   a.sd_out = (float*)take(sizeof(float) * 2 * (size_t)n_shared * hidden);
   a.act_amax = (unsigned*)take(sizeof(unsigned) * 2 * kSMaxTopK);
   a.tilesync = (unsigned*)take(sizeof(unsigned) * kTileCounters * (size_t)n_layers);
-  a.logits = (unsigned long long*)take(sizeof(unsigned long long) * 2 * (size_t)(experts + n_shared));
-  a.scores = (unsigned long long*)take(sizeof(unsigned long long) * 2 * (size_t)experts);
+  a.scores = (unsigned long long*)take(sizeof(unsigned long long) * 2 * (size_t)(experts + n_shared));
   a.activated = (uint16_t*)take(2 * 2 * (size_t)top_k * intermediate);
   a.shared_activated = (uint16_t*)take(2 * 2 * (size_t)n_shared * intermediate);
   a.residual = (uint16_t*)take(2 * 2 * (size_t)hidden);
   a.summed = (unsigned long long*)take(sizeof(unsigned long long) * 2 * (size_t)hidden);
   a.wait_limit = g_stack_wait_limit;
+  {
+    const char* pause = getenv("INKLING_STACK_POLL_PAUSE_NS");
+    a.poll_pause_ns = pause ? (unsigned)atoi(pause) : 500u;   // measured on B200: 250..2000 ns are equally good, 64 ns costs 4 us per block
+    if (a.poll_pause_ns > 100000u) a.poll_pause_ns = 500u;
+  }
+  {
+    const char* laps = getenv("INKLING_STACK_PREFETCH_LAPS");
+    a.prefetch_laps = laps ? atoi(laps) : 0;   // measured on B200: asking the L2 ahead of the ring makes the stream slower (0 is fastest)
+    if (a.prefetch_laps < 0 || a.prefetch_laps > 8) a.prefetch_laps = 0;
+  }
   for (int r = 0; r < kSMaxWorld; ++r) a.peer_inbox[r] = nullptr;
   for (int r = 0; r < world && world > 1; ++r) {
     char* region = (char*)(uintptr_t)peer_regions[r];

@@ -116,7 +116,10 @@ class StackDescriptor:
         region between two barriers, so that nobody stores into a region that is being cleared."""
         flags = self.status.clone()
         if self.world > 1:
-            torch.distributed.all_reduce(flags, op=torch.distributed.ReduceOp.BOR, group=self.group)
+            # (NCCL has no bitwise OR: the two bits are reduced apart, each with MAX)
+            bits = torch.stack([flags & 1, (flags >> 1) & 1]).to(torch.int32)
+            torch.distributed.all_reduce(bits, op=torch.distributed.ReduceOp.MAX, group=self.group)
+            flags = bits[0] | (bits[1] << 1)
         flags = int(flags.item())
         self.status.zero_()
         if flags & 2:
@@ -155,7 +158,7 @@ class StackDescriptor:
                    "shared_gate_up_everywhere", "shared_down_done", "routed_gate_up_everywhere", "activations_staged",
                    "routed_down_done", "down_everywhere", "norm_done", "x_digits_written", "producer_waits_for_routing",
                    "producer_has_routing", "producer_layer_issued", "x_digits_visible", "mma_gate_up_start", "mma_gate_up_end",
-                   "mma_down_start", "mma_down_end", "scales_gate_up_end", "scales_down_end", "", "")
+                   "mma_down_start", "mma_down_end", "scales_gate_up_end", "scales_down_end", "rows_sent", "norm_reduced")
 
     def trace(self) -> torch.Tensor:
         """Phase stamps of the last decode run with INKLING_STACK_TRACE=1: int64

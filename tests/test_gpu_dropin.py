@@ -13,7 +13,7 @@ from torch import nn
 
 import cases
 import reference_standin as rs
-from helpers import BF16, banks_to_device, max_rel
+from helpers import BF16, assert_router_matches, banks_to_device, max_rel
 from oracle import moe as oracle_moe
 from test_dropin_names import _load
 
@@ -95,12 +95,20 @@ def test_block_with_the_drop_in_matches_the_untouched_block(ib, device, plan):
             got = swapped(xs)
             torch.cuda.synchronize()
             assert got.shape == want.shape and got.dtype == want.dtype
-            # the untouched block multiplies BF16-dequantised weights with torch's BF16 GEMMs: same bar as the oracle
-            assert max_rel(got.float(), want.float()) <= TOL, (kind, plan, tokens)
+            same = torch.ones(tokens, dtype=torch.bool)
             if plan == "fused":
+                # the block's own router runs here too: tokens on which it and the untouched block's torch.topk
+                # pick different sets (a score tie or a logit on a BF16 rounding boundary) are compared with the
+                # oracle only, the others with the untouched block as well
                 mlp = swapped.layers[0].mlp
                 idx, w, gam = (t[:tokens].cpu() for t in (mlp.topk_indices, mlp.topk_weights, mlp.gammas))
+                assert_router_matches(p, x[:tokens], idx, w, gam)
                 assert max_rel(got[0].float(), oracle_moe.moe_layer_fp32(x[:tokens], p, banks, idx, w, gam)) <= TOL
+                theirs = model.layers[0].mlp.gate(xs)[2].cpu()
+                same = (theirs.sort(-1).values == idx.sort(-1).values).all(-1)
+                assert int(same.sum()) >= tokens - 2
+            # the untouched block multiplies BF16-dequantised weights with torch's BF16 GEMMs: same bar as the oracle
+            assert max_rel(got[0][same].float(), want[0][same].float()) <= TOL, (kind, plan, tokens)
     experts = swapped.layers[0].mlp.experts
     experts.check_status()
 
