@@ -212,6 +212,25 @@ int ink_expert_reduce(const void* down, const int64_t* indices, const void* weig
                       float* output, int tokens, int width, int top_k, int pointer_stride, int max_expert,
                       ink_stream_t stream);
 
+/* The grouped projection on the BLOCK-SCALED tensor-core path (same reference kernel, same outputs as
+ * ink_expert_gemm): the packed E2M1 codes of an expert's 128-row tile and their E4M3 block scales are the
+ * M operand of tcgen05.mma.kind::mxf4nvf4.block_scale.block16 straight from the checkpoint layout -- no
+ * conversion on the CUDA cores -- and the tokens routed to the expert are the N operand as four E2M1 digit
+ * rows each (power-of-two block scales; exact to 2^-9 of the block's largest magnitude), eight tokens per
+ * pass. Each active expert's bytes cross HBM once per eight of its tokens.
+ *  bank_maps  device copy (128-byte aligned) of the 512 bytes ink_moe_stack_encode_banks wrote for this
+ *             layer's banks, which must therefore be evenly spaced in memory; `start` is the expert id of
+ *             the first bank the descriptors cover (experts[g] - start indexes them)
+ *  pointers   as for ink_expert_gemm: the FP32 scale2 is read through it, a zero row skips the expert
+ *  scratch    ink_expert_gemm_tc_scratch_bytes(input_rows, k) bytes: a kernel in front writes every input row's
+ *             normaliser, digit rows and block scales there once; the main kernel reads them per expert tile
+ * Constraints: n a multiple of 128, k a multiple of 256 up to 4096, groups <= 1024. */
+size_t ink_expert_gemm_tc_scratch_bytes(int input_rows, int k);
+int ink_expert_gemm_tc(const void* x, int input_rows, const void* bank_maps, const int64_t* pointers,
+                       const int32_t* experts, const int32_t* rows, const int32_t* counts, void* y, int capacity,
+                       int n, int k, int top_k, int projection, int groups, int start, void* scratch,
+                       size_t scratch_bytes, int32_t* status, ink_stream_t stream);
+
 /* ------------------------------------------------- whole stack, one launch ------
  * One decode token through n_layers MoE blocks in ONE persistent cooperative kernel:
  * per block the router (as ink_router_forward), the expert plan (resolved to bank

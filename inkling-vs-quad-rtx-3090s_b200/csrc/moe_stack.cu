@@ -734,24 +734,6 @@ __device__ __forceinline__ void stage_x_tc(unsigned char* s_xdig, uint16_t* s_xb
   if (ct == 0) sh->x_inverse = inverse * (1.f / 512.f);
 }
 
-// Block scales of `rows` digit rows (`bytes_per_row` each, row r at table + r * pitch) into the
-// activation-scale columns of tensor memory, 4 columns per 64-element step. Four warps, one per
-// tensor-memory subpartition, write the same words.
-__device__ __forceinline__ void tc_upload_scales(uint32_t tmem, int subpartition, const uint8_t* table, int pitch, int rows, int steps,
-                                                 int lane) {
-  const uint32_t base = tmem + ((uint32_t)(subpartition * 32) << 16) + kTcColSfb;
-#pragma unroll 1
-  for (int s0 = 0; s0 < steps; s0 += 4) {
-    uint32_t r[16];
-#pragma unroll
-    for (int j = 0; j < 16; ++j)
-      r[j] = ((j & 3) == 0 && lane < rows) ? *reinterpret_cast<const uint32_t*>(table + (size_t)lane * pitch + (s0 + (j >> 2)) * 4) : 0u;
-    tc_st16(base + s0 * 4, r);
-  }
-  tc_wait_st();
-  tc_fence_before();
-}
-
 // ---- hand-over of the layer's output rows (the all-reduce of a block, for any number of ranks)
 // The thread that holds this rank's total of output row `row` stores it, tagged, where the rows are
 // summed: one rank -> straight into `summed`; several ranks -> into slot `rank` of every rank's inbox

@@ -163,6 +163,24 @@ __device__ __forceinline__ void tc_stage8(uint4 raw, float scale, unsigned char*
   }
 }
 
+// Block scales of `rows` digit rows (`bytes_per_row` each, row r at table + r * pitch) into the
+// activation-scale columns of tensor memory, 4 columns per 64-element step. Four warps, one per
+// tensor-memory subpartition, write the same words.
+__device__ __forceinline__ void tc_upload_scales(uint32_t tmem, int subpartition, const uint8_t* table, int pitch, int rows, int steps,
+                                                 int lane) {
+  const uint32_t base = tmem + ((uint32_t)(subpartition * 32) << 16) + kTcColSfb;
+#pragma unroll 1
+  for (int s0 = 0; s0 < steps; s0 += 4) {
+    uint32_t r[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      r[j] = ((j & 3) == 0 && lane < rows) ? *reinterpret_cast<const uint32_t*>(table + (size_t)lane * pitch + (s0 + (j >> 2)) * 4) : 0u;
+    tc_st16(base + s0 * 4, r);
+  }
+  tc_wait_st();
+  tc_fence_before();
+}
+
 // owner of item x when `total` items are dealt to `parts` blocks as [total*b/parts, total*(b+1)/parts)
 __device__ __forceinline__ int tc_owner(long long x, long long total, long long parts) { return (int)(((x + 1) * parts - 1) / total); }
 

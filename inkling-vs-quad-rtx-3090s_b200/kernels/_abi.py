@@ -34,6 +34,8 @@ _SIGNATURES = {
     "ink_expert_gemm_scratch_bytes": (Z, [I]),
     "ink_expert_gemm": (I, [P, I, P, P, P, P, P, I, I, I, I, I, I, I, P, Z, P, P]),
     "ink_expert_reduce": (I, [P, P, P, P, P, I, I, I, I, I, P]),
+    "ink_expert_gemm_tc_scratch_bytes": (Z, [I, I]),
+    "ink_expert_gemm_tc": (I, [P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P, Z, P, P]),
     "ink_moe_stack_layer_bytes": (Z, []),
     "ink_moe_stack_encode_banks": (I, [P, P, ctypes.c_uint64, P, ctypes.c_uint64, P, ctypes.c_uint64, P, ctypes.c_uint64, I, I, I]),
     "ink_moe_stack_scratch_bytes": (Z, [I, I, I, I, I, I]),

@@ -17,7 +17,7 @@ from __future__ import annotations
 import torch
 from torch import nn
 
-from .kernels import (StackDescriptor, expert_bank_names, expert_copy, expert_gemm, expert_plan, expert_reduce,
+from .kernels import (StackDescriptor, encode_bank_maps, expert_bank_names, expert_copy, expert_gemm, expert_plan, expert_reduce,
                       moe_decode, routed_decode, router_forward, router_plan_forward, router_workspace,
                       stack_supported)
 from .kernels.paired_all_reduce import all_reduce
@@ -82,6 +82,10 @@ class ResidentExperts(nn.Module):
         kinds = ("gate_up_proj", "gate_up_proj_scale", "down_proj", "down_proj_scale")
         self.bank_layout = self._even_spacing([[weights[e][n].data_ptr() for e in ids] for n in kinds],
                                               [first[n].numel() * first[n].element_size() for n in kinds]) if self.quantized else None
+        # TMA descriptors of the banks for the block-scaled grouped kernel, where they are evenly spaced
+        self.bank_maps = None
+        if self.bank_layout is not None and hidden_dim % 256 == 0 and intermediate_dim % 256 == 0:
+            self.bank_maps = encode_bank_maps(self.bank_layout, self.local, hidden_dim, intermediate_dim, self.device)
         self.resident = torch.ones(self.local, **i32)
         self.destinations = torch.zeros((0, self.stride), dtype=torch.int64, device=self.device)
         self.slot_experts = torch.full((0,), -1, **i32)
@@ -141,7 +145,8 @@ class ResidentExperts(nn.Module):
                     (1, self.activated, self.down, self.hidden_dim, self.intermediate_dim)):
                 grid = (triton_cdiv(routes, 16), triton_cdiv(n, 64), groups)
                 expert_gemm[grid](inputs, self.pointers, self.experts, self.rows, self.counts, target, self.capacity,
-                                  n, k, top_k, projection, True, self.stride, 16, 64, 64, status=self.status)
+                                  n, k, top_k, projection, True, self.stride, 16, 64, 64, status=self.status,
+                                  bank_maps=self.bank_maps, start=self.start)
             expert_reduce[(tokens, triton_cdiv(self.hidden_dim, 256))](
                 self.down, indices, weights, self.pointers, output, self.hidden_dim, top_k, self.stride,
                 self.max_expert, 256)

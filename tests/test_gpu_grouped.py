@@ -117,3 +117,52 @@ def test_batched_decode_64_tokens_zipf_at_full_shapes(ib, device):
             assert max_rel(got, want) <= TOL
             assert rel_floor(got, want) <= 0.2
         del cpu_banks
+
+
+@pytest.mark.parametrize("d,f,E,tokens", [(1024, 512, 32, 40), (2048, 256, 16, 24), (1024, 512, 32, 200)])
+def test_block_scaled_projections_against_oracle(ib, device, d, f, E, tokens):
+    """ink_expert_gemm_tc: the packed banks straight into tcgen05.mma.kind::mxf4nvf4.block_scale (banks of one
+    kind in one allocation, addressed through TMA descriptors), tokens as E2M1 digit rows; experts with more than
+    eight routes take several passes. Against the CPU oracle, and against the kernel that expands to FP16."""
+    k = 6
+    banks = ib.make_expert_banks(E, d, f, device, seed=17)
+    experts_module = ib.ResidentExperts(d, f, None, banks.weights)
+    assert experts_module.bank_maps is not None
+    gen = torch.Generator().manual_seed(tokens)
+    x = torch.randn(tokens, d, generator=gen).to(BF16)
+    idx = _skewed_routing(gen, tokens, E, k)
+    w = torch.rand(tokens, k, generator=gen).to(BF16)
+    routes = idx.numel()
+    capacity = 1 << (routes - 1).bit_length()
+    i32 = dict(dtype=torch.int32, device=device)
+    sources = experts_module.sources
+    pointers = torch.zeros(E * 6, dtype=torch.int64, device=device)
+    experts, counts = torch.empty(E, **i32), torch.empty(E, **i32)
+    rows = torch.full((E, capacity), -1, **i32)
+    idx_d, w_d, x_d = idx.to(device), w.to(device), x.to(device)
+    ib.kernels.expert_plan[(1,)](idx_d, sources, None, None, None, None, None, torch.empty(0, **i32), pointers,
+                                 experts, counts, rows, 0, E, 0, 6, routes, capacity)
+    groups = min(routes, E)
+    status = torch.zeros(1, **i32)
+    outs = {}
+    for name, maps in (("block_scaled", experts_module.bank_maps), ("fp16", None)):
+        activated = torch.zeros(capacity, f, dtype=BF16, device=device)
+        down = torch.zeros(capacity, d, dtype=BF16, device=device)
+        ib.kernels.expert_gemm[(1, 1, groups)](x_d, pointers, experts, rows, counts, activated, capacity, 2 * f, d, k,
+                                               0, True, 6, 16, 64, 64, status=status, bank_maps=maps)
+        ib.kernels.expert_gemm[(1, 1, groups)](activated, pointers, experts, rows, counts, down, capacity, d, f, k,
+                                               1, True, 6, 16, 64, 64, status=status, bank_maps=maps)
+        out = torch.zeros(tokens, d, dtype=torch.float32, device=device)
+        ib.kernels.expert_reduce[(tokens, 1)](down, idx_d, w_d, pointers, out, d, k, 6, E - 1, 256)
+        torch.cuda.synchronize()
+        outs[name] = (activated.cpu(), down.cpu(), out.cpu())
+    assert int(status.item()) == 0
+    cpu_banks = {e: {n: t.cpu() for n, t in banks.weights[e].items()} for e in range(E)}
+    plan = oracle_moe.expert_plan(idx, sources.cpu(), 0, E, 6, capacity)
+    activated, down, out = outs["block_scaled"]
+    want_act = oracle_moe.expert_gemm_reference(x, plan, cpu_banks, 0, k, 2 * f, capacity)
+    assert max_rel(activated.float(), want_act.float()) <= 1.6e-2
+    want_down = oracle_moe.expert_gemm_reference(activated, plan, cpu_banks, 1, k, d, capacity)
+    assert max_rel(down.float(), want_down.float()) <= 1.6e-2
+    assert max_rel(out, oracle_moe.routed_experts_fp32(x, idx, w, cpu_banks)) <= TOL
+    assert max_rel(out, outs["fp16"][2]) <= TOL
