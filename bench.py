@@ -366,6 +366,11 @@ def run_ours(args) -> None:
     if layers != args.layers:
         line["config"]["workload"] += f" (only {layers} blocks fit in free device memory)"
         line["config"]["layers"] = layers
+    if world == 1:
+        # configs[3] on four blocks of the same stack (outside the timed region): the grouped tensor-core path
+        # against the per-route GEMV at 64 tokens
+        line["batched"] = batched_numbers(ib, list(stack.layers[:4]), 3)["64"]
+        line["batched"]["workload"] = "configs[3]: one block, 64 tokens, Zipf(1.1) routing, routed experts only"
     if world == 1 and not args.no_cpu_baseline:
         seconds, times = time_cpu_layer(runs=10, warmup=2)
         cores = os.cpu_count() or 1
@@ -439,59 +444,76 @@ def self_check(ib, stack, runner, x, device, group, rank: int, world: int) -> di
             "max_rel": max_rel, "max_rel_floor": max_rel_floor, "ok": bool(max_rel <= 2e-2)}
 
 
+def batched_numbers(ib, layers, steps: int, token_counts=(64,)) -> dict:
+    """configs[3]: `tokens` tokens through ONE block of the full shapes, routing skewed by Zipf(1.1), routed experts
+    only: the grouped tensor-core path (block-scaled tcgen05 on the packed banks) against the per-route GEMV path on
+    the same routing. `layers` are rotated so that nothing is L2-warm. Per token count: milliseconds of both paths and
+    the weight bytes of the DISTINCT experts per second of the grouped path (each expert's 14 155 776 bytes once)."""
+    import torch
+
+    device = layers[0].router_weight.device
+    expert_bytes = 2 * INTERMEDIATE * HIDDEN // 2 + 2 * INTERMEDIATE * HIDDEN // 16 + HIDDEN * INTERMEDIATE // 2 + HIDDEN * INTERMEDIATE // 16
+    peaks, peak_kind = load_peaks()
+    out = {}
+    for tokens in token_counts:
+        gen = torch.Generator().manual_seed(7)
+        probs = 1.0 / torch.arange(1, EXPERTS + 1).float() ** 1.1
+        perm = torch.randperm(EXPERTS, generator=gen)
+        idx = torch.stack([perm[torch.multinomial(probs, TOP_K, replacement=False, generator=gen)] for _ in range(tokens)])
+        idx = idx.to(device)
+        w = torch.rand(tokens, TOP_K, generator=gen).to(torch.bfloat16).to(device)
+        x = torch.randn(tokens, HIDDEN, generator=gen).to(torch.bfloat16).to(device)
+        distinct = int(torch.unique(idx).numel())
+
+        def timed(fn):
+            for layer in layers:
+                fn(layer)
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(steps):
+                for layer in layers:
+                    fn(layer)
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / (steps * len(layers))
+
+        def grouped(layer):
+            ex = layer.experts
+            final = torch.zeros(tokens, HIDDEN, dtype=torch.float32, device=device)
+            ex._reserve(idx.numel())
+            ex._plan(idx)
+            ex._project_grouped(x, idx, w, final)
+
+        def gemv(layer):
+            for i in range(0, tokens, 8):
+                layer.experts(x[i:i + 8], idx[i:i + 8], w[i:i + 8])
+
+        grouped_ms, gemv_ms = timed(grouped), timed(gemv)
+        out[str(tokens)] = {
+            "tokens": tokens, "routes": tokens * TOP_K, "distinct_experts": distinct,
+            "grouped_tcgen05_ms": grouped_ms, "gemv_per_route_ms": gemv_ms, "speedup": gemv_ms / grouped_ms,
+            "grouped_weight_gbs": distinct * expert_bytes / (grouped_ms * 1e-3) / 1e9,
+            "frac_of_peak": distinct * expert_bytes / (grouped_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "peak_kind": peak_kind}
+    return out
+
+
 def run_batched(args) -> None:
-    """configs[3]: 64 tokens through ONE block of the full shapes, routing skewed by Zipf(1.1):
-    the grouped tensor-core path against the per-route GEMV path on the same routing. Prints its
-    own JSON line (not the headline metric)."""
+    """configs[3] on its own (not the headline metric): prints one JSON line with the sweep over token counts."""
     import torch
 
     import inkling_b200 as ib
 
     device = torch.device("cuda", 0)
     torch.cuda.set_device(0)
-    tokens = 64
     layers = [ib.MoEStack.synthetic(1, HIDDEN, INTERMEDIATE, EXPERTS, N_SHARED, TOP_K, device, seed=100 + i).layers[0]
-              for i in range(4)]          # rotate blocks so that nothing is L2-warm
-    gen = torch.Generator().manual_seed(7)
-    probs = 1.0 / torch.arange(1, EXPERTS + 1).float() ** 1.1
-    perm = torch.randperm(EXPERTS, generator=gen)
-    idx = torch.stack([perm[torch.multinomial(probs, TOP_K, replacement=False, generator=gen)] for _ in range(tokens)])
-    idx = idx.to(device)
-    w = torch.rand(tokens, TOP_K, generator=gen).to(torch.bfloat16).to(device)
-    x = torch.randn(tokens, HIDDEN, generator=gen).to(torch.bfloat16).to(device)
-    distinct = int(torch.unique(idx).numel())
-
-    def timed(fn):
-        for layer in layers:
-            fn(layer)
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(args.steps):
-            for layer in layers:
-                fn(layer)
-        b.record()
-        torch.cuda.synchronize()
-        return a.elapsed_time(b) / (args.steps * len(layers))
-
-    grouped_ms = timed(lambda layer: layer.experts(x, idx, w))
-
-    def gemv(layer):
-        for i in range(0, tokens, 8):
-            layer.experts(x[i:i + 8], idx[i:i + 8], w[i:i + 8])
-
-    gemv_ms = timed(gemv)
-    expert_bytes = 2 * INTERMEDIATE * HIDDEN // 2 + 2 * INTERMEDIATE * HIDDEN // 16 + HIDDEN * INTERMEDIATE // 2 + HIDDEN * INTERMEDIATE // 16
-    peaks, peak_kind = load_peaks()
+              for i in range(args.batched_blocks)]
+    numbers = batched_numbers(ib, layers, args.steps, token_counts=(9, 16, 32, 64))
     print(json.dumps({
-        "metric": "batched_decode_block_ms", "value": grouped_ms, "unit": "ms", "higher_is_better": False,
-        "n_gpus": 1, "steps": args.steps, "data": "synthetic",
-        "config": {"workload": "configs[3]: one block, 64 tokens, Zipf(1.1) routing, routed experts only",
-                   "tokens": tokens, "distinct_experts": distinct, "routes": tokens * TOP_K},
-        "grouped_tcgen05_ms": grouped_ms, "gemv_per_route_ms": gemv_ms,
-        "grouped_weight_gbs": distinct * expert_bytes / (grouped_ms * 1e-3) / 1e9,
-        "gemv_weight_gbs": tokens * TOP_K * expert_bytes / (gemv_ms * 1e-3) / 1e9,
-        "peak_gbs": peaks["hbm_gbs"], "peak_kind": peak_kind}), flush=True)
+        "metric": "batched_decode_block_ms", "value": numbers["64"]["grouped_tcgen05_ms"], "unit": "ms",
+        "higher_is_better": False, "n_gpus": 1, "steps": args.steps, "data": "synthetic",
+        "config": {"workload": "configs[3]: one block, 64 tokens, Zipf(1.1) routing, routed experts only"},
+        "by_tokens": numbers}), flush=True)
 
 
 def leave(world: int) -> None:
@@ -513,6 +535,7 @@ def main() -> None:
     parser.add_argument("--no-graph", action="store_true", help="eager launches instead of graph replay")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--batched", action="store_true", help="configs[3] instead of the headline workload")
+    parser.add_argument("--batched-blocks", type=int, default=4, help="blocks rotated by --batched (1 for a profiler capture)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.batched:

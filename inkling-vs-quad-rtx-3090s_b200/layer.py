@@ -138,24 +138,29 @@ class ResidentExperts(nn.Module):
         (my_inkling/offloaded_experts.py:224-296). `output` must be zero on entry."""
         tokens = x.shape[0]
         if tokens > MATVEC_TOKENS and self.grouped_supported():
-            routes, top_k = indices.numel(), indices.shape[1]
-            groups = min(routes, self.local)
-            for projection, inputs, target, n, k in (
-                    (0, x, self.activated, 2 * self.intermediate_dim, self.hidden_dim),
-                    (1, self.activated, self.down, self.hidden_dim, self.intermediate_dim)):
-                grid = (triton_cdiv(routes, 16), triton_cdiv(n, 64), groups)
-                expert_gemm[grid](inputs, self.pointers, self.experts, self.rows, self.counts, target, self.capacity,
-                                  n, k, top_k, projection, True, self.stride, 16, 64, 64, status=self.status,
-                                  bank_maps=self.bank_maps, start=self.start)
-            expert_reduce[(tokens, triton_cdiv(self.hidden_dim, 256))](
-                self.down, indices, weights, self.pointers, output, self.hidden_dim, top_k, self.stride,
-                self.max_expert, 256)
+            self._project_grouped(x, indices, weights, output)
             return
         for t0 in range(0, tokens, MATVEC_TOKENS):
             t1 = min(tokens, t0 + MATVEC_TOKENS)
             routed_decode(x[t0:t1], indices[t0:t1], weights[t0:t1], self.pointers,
                           self.activated[t0 * indices.shape[1]:], output[t0:t1], self.max_expert, self.quantized,
                           status=self.status)
+
+    def _project_grouped(self, x, indices, weights, output) -> None:
+        """Both projections as grouped tensor-core GEMMs over the plan's groups, then the weighted
+        sum per token (my_inkling/offloaded_experts.py:249-296). `output` must be zero on entry."""
+        tokens, routes, top_k = x.shape[0], indices.numel(), indices.shape[1]
+        groups = min(routes, self.local)
+        for projection, inputs, target, n, k in (
+                (0, x, self.activated, 2 * self.intermediate_dim, self.hidden_dim),
+                (1, self.activated, self.down, self.hidden_dim, self.intermediate_dim)):
+            grid = (triton_cdiv(routes, 16), triton_cdiv(n, 64), groups)
+            expert_gemm[grid](inputs, self.pointers, self.experts, self.rows, self.counts, target, self.capacity,
+                              n, k, top_k, projection, True, self.stride, 16, 64, 64, status=self.status,
+                              bank_maps=self.bank_maps, start=self.start)
+        expert_reduce[(tokens, triton_cdiv(self.hidden_dim, 256))](
+            self.down, indices, weights, self.pointers, output, self.hidden_dim, top_k, self.stride,
+            self.max_expert, 256)
 
     def forward(self, hidden_states, top_k_index, top_k_weights):
         final = torch.zeros_like(hidden_states, dtype=torch.float32)
