@@ -141,7 +141,6 @@ struct StackArgs {
   long long wait_limit;            // SM clocks a wait may take before the launch gives up
   unsigned poll_pause_ns;          // pause between two polls of a hand-over word
   int prefetch_laps;               // laps of the ring a tile is requested from the L2 ahead of its copy (0: no prefetch)
-  int prefetch_next;               // laps of the NEXT layer's first tiles (beyond those the ring will hold) requested from the L2
                                    // when a lane issues its last tile of a layer: they arrive while the blocks hand their rows over
   int32_t* status;
   unsigned long long* trace;       // optional [n_layers][kTraceBlocks][kTraceSlots] nanosecond stamps
@@ -658,7 +657,7 @@ __device__ __forceinline__ void stage_x(uint16_t* s_x16, uint16_t* s_xbf, const 
     for (int g = 0; g < V::VG; ++g) {
       const int group = g * V::VT + ct;
       reinterpret_cast<uint4*>(s_xbf)[group] = xb[g];
-      const uint4 h = stage_pack8(xb[g], scale);
+      const uint4 h = stage_pack8(xb[g], scale, ct & 3);   // group g * VT + ct of eight values, VT a multiple of 32
       reinterpret_cast<uint4*>(s_x16)[group] = h;
     }
   }
@@ -1041,17 +1040,6 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
         if (d.first_bytes) bulk_g2s(dst, d.first, d.first_bytes, bar);
         if (d.second_bytes) bulk_g2s(dst + d.second_at, d.second, d.second_bytes, bar);
         if (t == plan.s_pad - 1) INK_TRACE(layer, kTrProdLayerIssued);
-        if (a.prefetch_next > 0 && t + kSStages >= plan.per_layer && layer + 1 < a.n_layers) {
-          // this lane's last tile of the layer: the memory system is about to go idle while the rows are handed
-          // over and normalised, so ask it for the next layer's tiles beyond the ring's reach (none of them routed)
-          for (int k = 1; k <= a.prefetch_next; ++k) {
-            const int nt = lane + k * kSStages;
-            if (nt < plan.s_qg && describe(layer + 1, nt, d)) {
-              if (d.first_bytes) bulk_prefetch_l2(d.first, d.first_bytes);
-              if (d.second_bytes) bulk_prefetch_l2(d.second, d.second_bytes);
-            }
-          }
-        }
       }
     }
   } else if (warp == 0) {
@@ -2367,9 +2355,6 @@ static int stack_decode(const void* layers, int n_layers, const void* x, void* r
   }
   {
     const char* laps = getenv("INKLING_STACK_PREFETCH_LAPS");
-    const char* next = getenv("INKLING_STACK_PREFETCH_NEXT");
-    a.prefetch_next = next ? atoi(next) : 0;
-    if (a.prefetch_next < 0 || a.prefetch_next > 8) a.prefetch_next = 0;
     a.prefetch_laps = laps ? atoi(laps) : 0;   // measured on B200: asking the L2 ahead of the ring makes the stream slower (0 is fastest)
     if (a.prefetch_laps < 0 || a.prefetch_laps > 8) a.prefetch_laps = 0;
   }

@@ -8,6 +8,8 @@
 #include "../../include/inkling_b200.h"
 #include "common.cuh"
 #include "decode_args.cuh"
+// this file stages its activations itself, in natural order: every word decoded with the conversion instruction
+#define INK_E2M1_ON_ALU 0
 #include "stream_math.cuh"
 
 namespace ink {

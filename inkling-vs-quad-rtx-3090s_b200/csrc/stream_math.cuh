@@ -11,12 +11,22 @@ namespace ink {
 // 2^-14 (the code's subnormal 0.5 lands on an FP16 subnormal), so a shift and a mask per field
 // decode two codes at once; the staged activations carry the 2^14 back (see stage_pack8) and are
 // permuted so that the codes j and j+4 of a word share a register with their activations.
-// Measured on B200: the conversion instruction sustains one per ~3 cycles per scheduler, the 15
-// logic operations of a word ~17 cycles against ~12 for its four conversions, and the one-launch
-// kernel runs 10 % slower on the logic path. It stays as a switch for parts where that differs.
+// Measured on B200 in the one-launch kernel (4096 x 2048, one GPU, per block of the stack):
+//   0: every word with the conversion instruction                      48.9 us
+//   1: every word with logic (15 operations a word against 4)          56.7 us
+//   2: words 0, 1 of a 16-byte group converted, words 2, 3 with logic  53.3 us
+// The conversions run on the XU pipe and keep it busy for 3/4 of the kernel's time, yet moving work
+// from it to the integer pipe only costs: the consumer warps hold a ring slot for as long as they
+// compute on it, and every instruction more keeps bytes out of flight. The switch stays for parts
+// where the balance differs.
 #ifndef INK_E2M1_ON_ALU
 #define INK_E2M1_ON_ALU 0
 #endif
+
+// whether word `word` (0..3) of a 16-byte group of codes is decoded with integer logic
+__host__ __device__ constexpr bool e2m1_word_on_alu(int word) {
+  return INK_E2M1_ON_ALU == 1 || (INK_E2M1_ON_ALU == 2 && (word & 2) != 0);
+}
 
 // eight codes of a word -> four f16x2: h[j] = (code j, code j + 4), each times 2^-14
 __device__ __forceinline__ void e2m1x8_alu(uint32_t w, uint32_t (&h)[4]) {
@@ -25,28 +35,28 @@ __device__ __forceinline__ void e2m1x8_alu(uint32_t w, uint32_t (&h)[4]) {
   h[2] = ((w << 1) & 0x0E000E00u) | ((w << 4) & 0x80008000u);
   h[3] = ((w >> 3) & 0x0E000E00u) | (w & 0x80008000u);
 }
+template <bool ALU>
 __device__ __forceinline__ void e2m1x8_decode(uint32_t w, uint32_t (&h)[4]) {
-#if INK_E2M1_ON_ALU
-  e2m1x8_alu(w, h);
-#else
-  e2m1x8_to_f16x2(w, h);
-#endif
+  if constexpr (ALU) e2m1x8_alu(w, h);
+  else e2m1x8_to_f16x2(w, h);
 }
-// eight consecutive BF16 activations times `scale` -> eight FP16 in the order dot32 wants them
-__device__ __forceinline__ uint4 stage_pack8(const uint4& v, float scale) {
+
+// eight consecutive BF16 activations times `scale` -> eight FP16 in the order dot32 wants them for
+// word `word` (0..3) of their group of 32
+__device__ __forceinline__ uint4 stage_pack8(const uint4& v, float scale, int word) {
   uint4 h;
-#if INK_E2M1_ON_ALU
-  const float s = scale * 16384.f;   // the decoded weights are 2^-14 too small
-  h.x = f32x2_to_f16x2(bf16lo(v.x) * s, bf16lo(v.z) * s);   // (x0, x4)
-  h.y = f32x2_to_f16x2(bf16hi(v.x) * s, bf16hi(v.z) * s);   // (x1, x5)
-  h.z = f32x2_to_f16x2(bf16lo(v.y) * s, bf16lo(v.w) * s);   // (x2, x6)
-  h.w = f32x2_to_f16x2(bf16hi(v.y) * s, bf16hi(v.w) * s);   // (x3, x7)
-#else
-  h.x = f32x2_to_f16x2(bf16lo(v.x) * scale, bf16hi(v.x) * scale);
-  h.y = f32x2_to_f16x2(bf16lo(v.y) * scale, bf16hi(v.y) * scale);
-  h.z = f32x2_to_f16x2(bf16lo(v.z) * scale, bf16hi(v.z) * scale);
-  h.w = f32x2_to_f16x2(bf16lo(v.w) * scale, bf16hi(v.w) * scale);
-#endif
+  if (e2m1_word_on_alu(word)) {
+    const float s = scale * 16384.f;   // the decoded weights are 2^-14 too small
+    h.x = f32x2_to_f16x2(bf16lo(v.x) * s, bf16lo(v.z) * s);   // (x0, x4)
+    h.y = f32x2_to_f16x2(bf16hi(v.x) * s, bf16hi(v.z) * s);   // (x1, x5)
+    h.z = f32x2_to_f16x2(bf16lo(v.y) * s, bf16lo(v.w) * s);   // (x2, x6)
+    h.w = f32x2_to_f16x2(bf16hi(v.y) * s, bf16hi(v.w) * s);   // (x3, x7)
+  } else {
+    h.x = f32x2_to_f16x2(bf16lo(v.x) * scale, bf16hi(v.x) * scale);
+    h.y = f32x2_to_f16x2(bf16lo(v.y) * scale, bf16hi(v.y) * scale);
+    h.z = f32x2_to_f16x2(bf16lo(v.z) * scale, bf16hi(v.z) * scale);
+    h.w = f32x2_to_f16x2(bf16lo(v.w) * scale, bf16hi(v.w) * scale);
+  }
   return h;
 }
 
@@ -54,13 +64,13 @@ __device__ __forceinline__ uint4 stage_pack8(const uint4& v, float scale) {
 __device__ __forceinline__ float dot32(const uint4& q, uint32_t scale_pair, const uint32_t* x) {
   uint32_t h[4];
   uint32_t a0 = 0u, a1 = 0u;
-  e2m1x8_decode(q.x, h);
+  e2m1x8_decode<e2m1_word_on_alu(0)>(q.x, h);
   a0 = hfma2(h[0], x[0], a0); a0 = hfma2(h[1], x[1], a0); a0 = hfma2(h[2], x[2], a0); a0 = hfma2(h[3], x[3], a0);
-  e2m1x8_decode(q.y, h);
+  e2m1x8_decode<e2m1_word_on_alu(1)>(q.y, h);
   a0 = hfma2(h[0], x[4], a0); a0 = hfma2(h[1], x[5], a0); a0 = hfma2(h[2], x[6], a0); a0 = hfma2(h[3], x[7], a0);
-  e2m1x8_decode(q.z, h);
+  e2m1x8_decode<e2m1_word_on_alu(2)>(q.z, h);
   a1 = hfma2(h[0], x[8], a1); a1 = hfma2(h[1], x[9], a1); a1 = hfma2(h[2], x[10], a1); a1 = hfma2(h[3], x[11], a1);
-  e2m1x8_decode(q.w, h);
+  e2m1x8_decode<e2m1_word_on_alu(3)>(q.w, h);
   a1 = hfma2(h[0], x[12], a1); a1 = hfma2(h[1], x[13], a1); a1 = hfma2(h[2], x[14], a1); a1 = hfma2(h[3], x[15], a1);
   // The two block sums are added in FP16 (b = (a0.lo + a0.hi, a1.lo + a1.hi)) and multiplied by their
   // E4M3 scales with FP32-accumulating mixed-precision FMAs.
@@ -138,7 +148,7 @@ __device__ __forceinline__ float warp_stage_f16(const uint16_t* src, uint16_t* d
   const float scale = pow2_normaliser(amax, &inverse);
 #pragma unroll
   for (int n = 0; n < N; ++n) {
-    const uint4 h = stage_pack8(v[n], scale);
+    const uint4 h = stage_pack8(v[n], scale, lane & 3);   // group n * 32 + lane of eight: word (lane & 3) of its 32
     reinterpret_cast<uint4*>(dst)[n * 32 + lane] = h;
   }
   return inverse;
