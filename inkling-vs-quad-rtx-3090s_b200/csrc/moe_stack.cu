@@ -40,6 +40,7 @@ namespace ink {
 
 constexpr int kSC = 8;                                 // consumer warps
 constexpr int kSStages = 2 * kSC;                      // ring slots
+constexpr unsigned kProducerLanes = (1u << kSStages) - 1u;   // the lanes of the producer warp that own a slot
 constexpr int kSSlot = 9216;                           // bytes per slot
 constexpr int kSThreads = (kSC + 2) * 32;              // producer + consumers + auxiliary
 constexpr int kSThreadsTc = (kSC + 2 + 8) * 32;        // tensor-core variant: + 4 warps that write weight scales, 4 that read accumulators
@@ -52,7 +53,7 @@ constexpr int kSMaxWorld = 8;                          // tensor-parallel ranks
 constexpr int kTileCountersPerLayer = kSMaxTopK * 32 + 32;   // routed gate/up tiles (at most 8 x 32), then down row tiles
 
 constexpr int kTraceBlocks = 256;
-constexpr int kTraceSlots = 24;
+constexpr int kTraceSlots = 32;
 // phase stamps written by consumer warp 0 (and slot 12..14 by the producer) when tracing is on
 enum TraceSlot {
   kTrLayerStart = 0, kTrRouterDone = 1, kTrShGuDone = 2, kTrRtGuDone = 3, kTrShGuAll = 4, kTrShDownDone = 5,
@@ -62,12 +63,21 @@ enum TraceSlot {
   kTrMmaGuStart = 16, kTrMmaGuEnd = 17, kTrMmaDownStart = 18, kTrMmaDownEnd = 19,   // the issuing thread
   kTrScalesGuEnd = 20, kTrScalesDownEnd = 21,                                // first warp that writes weight scales
   kTrRowsSent = 22, kTrNormReduced = 23,                                     // the warp that hands the block's rows over; consumers
+  // not stamps but SM clock cycles that consumer warp 0 spent waiting for tiles in each section of the layer
+  // (CUDA-core variant), and that producer lane 0 spent with a tile to issue but no free slot
+  kTrWaitRouter = 24, kTrWaitShGu = 25, kTrWaitRtGu = 26, kTrWaitShDown = 27, kTrWaitRtDown = 28, kTrProdSlotWait = 29,
+  kTrBusyShGu = 30, kTrBusyRtGu = 31,   // cycles consumer warp 0 held tiles of the shared / routed gate/up section
 };
 __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+#define INK_TRACE_VALUE(layer, slot, value)                                                             \
+  do {                                                                                                  \
+    if (a.trace && blockIdx.x < kTraceBlocks)                                                           \
+      a.trace[((size_t)(layer) * kTraceBlocks + blockIdx.x) * kTraceSlots + (slot)] = (value);          \
+  } while (0)
 #define INK_TRACE(layer, slot)                                                                          \
   do {                                                                                                  \
     if (a.trace && blockIdx.x < kTraceBlocks)                                                           \
@@ -140,7 +150,6 @@ struct StackArgs {
   unsigned long long* summed;      // scratch [2][hidden] tagged words: the rows summed over the ranks, for every block of this rank
   long long wait_limit;            // SM clocks a wait may take before the launch gives up
   unsigned poll_pause_ns;          // pause between two polls of a hand-over word
-  int prefetch_laps;               // laps of the ring a tile is requested from the L2 ahead of its copy (0: no prefetch)
                                    // when a lane issues its last tile of a layer: they arrive while the blocks hand their rows over
   int32_t* status;
   unsigned long long* trace;       // optional [n_layers][kTraceBlocks][kTraceSlots] nanosecond stamps
@@ -915,11 +924,13 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
     // A single thread issues about two tiles per microsecond (a wait on the slot's barrier, the
     // transaction count, two bulk copies: each a long-latency instruction), which caps one block at
     // ~18 KB/us, a third of its share of the HBM bandwidth. So lane s of this warp owns ring slot s
-    // and issues the tiles s, s + 16, ... of the block's whole sequence on its own; the tile's place
-    // in the layer is worked out from its index (the divisions run on sixteen lanes at once).
+    // and issues the tiles s, s + 16, ... of the block's whole sequence. The lanes run ONE loop
+    // together: each tests its own slot (and its layer's routing) without blocking, and those that can
+    // go work out their tile's place in the layer and issue it side by side. Lanes that each sat in a
+    // blocking wait of their own would take turns, one lane's instructions at a time, and the warp
+    // would again issue little more than a single thread.
     if (lane < kSStages) {
       constexpr int kQgPerJob = 2 * F / S::QG_ROWS;
-      const int kAhead = a.prefetch_laps * kSStages;   // tiles between a tile's prefetch into L2 and its copy into the ring
       const long long n_total = (long long)a.n_layers * plan.per_layer;
       unsigned char* dst = slots + (size_t)lane * kSSlot;
       uint64_t* bar = &sh.full[lane];
@@ -999,47 +1010,54 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
         }   // else: padding up to a multiple of the consumer count
         return true;
       };
-      int layer = 0, t = lane;                 // the tile to copy
-      int ahead_layer = 0, ahead_t = lane;     // the tile to prefetch, kAhead further on
-      for (int k = 0; k < kAhead / kSStages; ++k) {   // the first tiles are copied without having been prefetched
-        ahead_t += kSStages;
-        while (ahead_t >= plan.per_layer) {
-          ahead_t -= plan.per_layer;
-          ++ahead_layer;
+      int layer = 0, t = lane;   // the tile to copy
+      long long i = lane;        // its index in the block's whole sequence
+      int asked = -1;            // (trace) the last layer whose routing this lane asked for
+      long long stalled_since = clock64();
+      long long slot_wait = 0, looked_at = clock64();   // (tracing, lane 0)
+      while (true) {
+        const bool more = i < n_total;
+        if (!__any_sync(kProducerLanes, more)) break;
+        if (__any_sync(kProducerLanes, sh.failed != 0)) break;
+        bool ready = more;
+        if (ready && ((t >= plan.s_qg && t < plan.s_sd) || (t >= plan.s_qd && t < plan.s_pad))) {
+          if (t == plan.s_qg && asked != layer) {
+            INK_TRACE(layer, kTrProdRouteWait);
+            asked = layer;
+          }
+          ready = sh.routed_layers > layer;   // a routed tile: its layer's routing table must be there
         }
-      }
-      for (long long i = lane; i < n_total; i += kSStages, t += kSStages, ahead_t += kSStages) {
-        while (t >= plan.per_layer) {
-          t -= plan.per_layer;
-          ++layer;
+        if (ready && i >= kSStages) ready = mbar_test_wait(&sh.empty[lane], (uint32_t)((i / kSStages) - 1) & 1);
+        if (ready) {
+          __threadfence_block();
+          if (t == plan.s_qg) INK_TRACE(layer, kTrProdRouteGot);
+          Tile d;
+          describe(layer, t, d);
+          mbar_expect_tx(bar, d.first_bytes + d.second_bytes);
+          if (d.first_bytes) bulk_g2s(dst, d.first, d.first_bytes, bar);
+          if (d.second_bytes) bulk_g2s(dst + d.second_at, d.second, d.second_bytes, bar);
+          if (t == plan.s_pad - 1) INK_TRACE(layer, kTrProdLayerIssued);
+          if (lane == 0 && t + kSStages >= plan.per_layer) {
+            INK_TRACE_VALUE(layer, kTrProdSlotWait, (unsigned long long)slot_wait);
+            slot_wait = 0;
+          }
+          i += kSStages;
+          t += kSStages;
+          while (t >= plan.per_layer) {
+            t -= plan.per_layer;
+            ++layer;
+          }
+          stalled_since = clock64();
+        } else if (more && clock64() - stalled_since > sh.limit) {
+          sh.failed = 1;   // nothing for this lane within the limit: every wait of the launch gives up
         }
-        while (ahead_t >= plan.per_layer) {
-          ahead_t -= plan.per_layer;
-          ++ahead_layer;
+        if (a.trace && lane == 0 && more) {   // cycles with a tile to issue, its routing known, but the slot still in use
+          const long long now = clock64();
+          const bool routing_known = !((t >= plan.s_qg && t < plan.s_sd) || (t >= plan.s_qd && t < plan.s_pad)) || sh.routed_layers > layer;
+          if (!ready && routing_known) slot_wait += now - looked_at;
+          looked_at = now;
         }
-        if (sh.failed) break;
-        Tile d;
-        // Ask the L2 for the tile two laps of the ring ahead: the copy into the ring then finds it there, so
-        // the bytes in flight to HBM are no longer bounded by the ring (eight slots of it are in use by the
-        // consumers at any time), and the stream goes on while the consumers stand at a grid-wide hand-over.
-        if (kAhead > 0 && ahead_layer < a.n_layers && describe(ahead_layer, ahead_t, d)) {
-          if (d.first_bytes) bulk_prefetch_l2(d.first, d.first_bytes);
-          if (d.second_bytes) bulk_prefetch_l2(d.second, d.second_bytes);
-        }
-        if (t == plan.s_qg) INK_TRACE(layer, kTrProdRouteWait);
-        if ((t >= plan.s_qg && t < plan.s_sd) || (t >= plan.s_qd && t < plan.s_pad)) {
-          if (!wait_routing(layer, &sh)) break;
-        }
-        if (t == plan.s_qg) INK_TRACE(layer, kTrProdRouteGot);
-        describe(layer, t, d);
-        if (i >= kSStages && !mbar_wait(&sh.empty[lane], (uint32_t)((i / kSStages) - 1) & 1, sh.limit)) {
-          sh.failed = 1;
-          break;
-        }
-        mbar_expect_tx(bar, d.first_bytes + d.second_bytes);
-        if (d.first_bytes) bulk_g2s(dst, d.first, d.first_bytes, bar);
-        if (d.second_bytes) bulk_g2s(dst + d.second_at, d.second, d.second_bytes, bar);
-        if (t == plan.s_pad - 1) INK_TRACE(layer, kTrProdLayerIssued);
+        if (!__any_sync(kProducerLanes, ready)) __nanosleep(32);   // nothing to issue anywhere: leave the scheduler to the consumers
       }
     }
   } else if (warp == 0) {
@@ -1299,6 +1317,8 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
     long long base = 0;   // index of this layer's first tile in the block's whole sequence
 
     // first tile index >= start that belongs to this consumer (tile t belongs to consumer t % kSC)
+    long long waited = 0;   // (tracing) cycles this warp waited for tiles since the last section stamp
+    long long busy = 0, tile_from = 0;   // (tracing) cycles between a tile's arrival and its release
     auto first_of = [&](int start) -> int { return start + (cw - start % kSC + kSC) % kSC; };
     auto take = [&](int t, const unsigned char*& src, int& slot) -> bool {
       const long long i = base + t;
@@ -1308,7 +1328,12 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
         if (ok && lane == 0) ok = tc_wait_issued(i, &sh);
         ok = __all_sync(0xffffffffu, ok);
       }
+      const long long wait_from = a.trace ? clock64() : 0;
       if (ok) ok = mbar_wait(&sh.full[slot], (uint32_t)(i / kSStages) & 1, sh.limit);
+      if (a.trace) {
+        tile_from = clock64();
+        waited += tile_from - wait_from;
+      }
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
         sh.failed = 1;
@@ -1320,6 +1345,7 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
     auto release = [&](int slot) {
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh.empty[slot]);
+      if (a.trace) busy += clock64() - tile_from;
     };
     // one more tile of `section` (0 shared g/u, 1 routed g/u, 2 down) of this block is done;
     // returns true in the warp that finished the section's last tile
@@ -1335,6 +1361,21 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
       }
       done = __shfl_sync(0xffffffffu, done, 0);
       return done == n_tiles;
+    };
+    // The same per WARP: called once by each warp that has tiles in `section`, after its last one; `warps` is
+    // how many such warps the block has. (A shared-memory atomic with its answer and a shuffle cost ~500 cycles
+    // next to a tile's 1200..2000, and the consumers are what the kernel waits for: so not once per tile.)
+    auto warp_done = [&](int layer, int section, int warps, bool fence) -> bool {
+      int done = 0;
+      __syncwarp();
+      if (lane == 0) {
+        if (fence) __threadfence();
+        else __threadfence_block();
+        done = atomicAdd(&sh.done[layer & 1][section], 1) + 1;
+        __threadfence_block();
+      }
+      done = __shfl_sync(0xffffffffu, done, 0);
+      return done == warps;
     };
 
     const int sub = warp & 3;   // the tensor-memory subpartition this warp can reach
@@ -1422,6 +1463,8 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
         }
       }
       if (tracer) INK_TRACE(layer, kTrRouterDone);
+      if (tracer) INK_TRACE_VALUE(layer, kTrWaitRouter, (unsigned long long)waited);
+      waited = busy = 0;
       // ------------------------------------------------ shared gate/up
       {
         float g[S::SG_PAIRS], u[S::SG_PAIRS];
@@ -1465,10 +1508,13 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
           } else {
             release(slot);
           }
-          if (section_done(layer, 0, plan.n_sg, t + kSC >= plan.s_qg) && lane == 0) red_release_add(sync + kShGuDone, 1u);
+          if (t + kSC >= plan.s_qg && warp_done(layer, 0, min(kSC, plan.n_sg), true) && lane == 0) red_release_add(sync + kShGuDone, 1u);
         }
       }
       if (tracer) INK_TRACE(layer, kTrShGuDone);
+      if (tracer) INK_TRACE_VALUE(layer, kTrWaitShGu, (unsigned long long)waited);
+      if (tracer) INK_TRACE_VALUE(layer, kTrBusyShGu, (unsigned long long)busy);
+      waited = busy = 0;
       if (tc) {
         // this block is done with the BF16 copy of x: the tensor-core warps may overwrite it later on
         consumer_sync();
@@ -1523,10 +1569,13 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
           } else {
             release(slot);
           }
-          if (section_done(layer, 1, plan.n_q, t + kSC >= plan.s_sd) && lane == 0) red_release_add(sync + kRtGuDone, 1u);
+          if (t + kSC >= plan.s_sd && warp_done(layer, 1, min(kSC, plan.n_q), true) && lane == 0) red_release_add(sync + kRtGuDone, 1u);
         }
       }
       if (tracer) INK_TRACE(layer, kTrRtGuDone);
+      if (tracer) INK_TRACE_VALUE(layer, kTrWaitRtGu, (unsigned long long)waited);
+      if (tracer) INK_TRACE_VALUE(layer, kTrBusyRtGu, (unsigned long long)busy);
+      waited = busy = 0;
       // The phases that follow are not separated by block-wide barriers: a warp that is done with its gate/up
       // tiles goes on with its down tiles, and waits only for the staging flag of the vector it needs. Only
       // where the shared experts' staging area overlaps the x staging (narrow experts) must every warp be
@@ -1567,6 +1616,7 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
         }
       }
       unsigned sact_seen = 0;
+      bool last_of_block = false;   // this warp reported the block's last down tile (CUDA-core variant)
       for (int t = first_of(plan.s_sd); t < plan.s_qd; t += kSC) {
         const unsigned char* src;
         int slot;
@@ -1605,8 +1655,8 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
         }
         release(slot);
         if (!tc) {
-          // down tiles are counted together (shared + routed)
-          section_done(layer, 2, plan.n_sd + plan.n_qd, false);
+          // the warps are counted once for all their down tiles (shared + routed): here only by a warp without routed ones
+          if (t + kSC >= plan.s_pad && warp_done(layer, 2, min(kSC, plan.n_sd + plan.n_qd), false)) last_of_block = true;
         } else if (section_done(layer, 2, plan.n_sd_real, t + kSC >= plan.s_sd + plan.n_sd_real) && !sh.failed) {
           // the block's shared-expert rows are in global memory: count the block at every 128-row tile it
           // touches; whoever completes a tile (this warp or a tensor-core epilogue) sums and delivers it
@@ -1625,6 +1675,8 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
         }
       }
       if (tracer) INK_TRACE(layer, kTrShDownDone);
+      if (tracer) INK_TRACE_VALUE(layer, kTrWaitShDown, (unsigned long long)waited);
+      waited = 0;
       if constexpr (!tc) {
       // ------------------------------------------------ routed down
       wait_flag(&sh.seen[1], layer, &sh, lane);
@@ -1645,7 +1697,6 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
         const int sl = lane % S::LPR, rp = lane / S::LPR;
         uint32_t xr[S::QD_CPL][16];
         int loaded = -1;
-        bool last_of_block = false;
         for (int t = first_of(plan.s_qd); t < plan.s_pad; t += kSC) {
           const unsigned char* src;
           int slot;
@@ -1718,7 +1769,7 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
           } else {
             release(slot);
           }
-          if (section_done(layer, 2, plan.n_sd + plan.n_qd, false)) last_of_block = true;
+          if (t + kSC >= plan.s_pad && warp_done(layer, 2, min(kSC, plan.n_sd + plan.n_qd), false)) last_of_block = true;
         }
         // The warp that finished the block's last down tile sums the contributions in a
         // fixed order (routes in choice order, then the shared experts) and publishes them.
@@ -1747,6 +1798,8 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
         release(slot);
       }
       if (tracer) INK_TRACE(layer, kTrRtDownDone);
+      if (tracer) INK_TRACE_VALUE(layer, kTrWaitRtDown, (unsigned long long)waited);
+      waited = 0;
       const unsigned long long* summed = a.summed + (size_t)xpar * D;
       if (!a.glue) {
         // one block only: each block writes its own rows, summed over the ranks, as they arrive
@@ -2352,11 +2405,6 @@ static int stack_decode(const void* layers, int n_layers, const void* x, void* r
     const char* pause = getenv("INKLING_STACK_POLL_PAUSE_NS");
     a.poll_pause_ns = pause ? (unsigned)atoi(pause) : 500u;   // measured on B200: 250..2000 ns are equally good, 64 ns costs 4 us per block
     if (a.poll_pause_ns > 100000u) a.poll_pause_ns = 500u;
-  }
-  {
-    const char* laps = getenv("INKLING_STACK_PREFETCH_LAPS");
-    a.prefetch_laps = laps ? atoi(laps) : 0;   // measured on B200: asking the L2 ahead of the ring makes the stream slower (0 is fastest)
-    if (a.prefetch_laps < 0 || a.prefetch_laps > 8) a.prefetch_laps = 0;
   }
   for (int r = 0; r < kSMaxWorld; ++r) a.peer_inbox[r] = nullptr;
   for (int r = 0; r < world && world > 1; ++r) {

@@ -158,12 +158,15 @@ class StackDescriptor:
                    "shared_gate_up_everywhere", "shared_down_done", "routed_gate_up_everywhere", "activations_staged",
                    "routed_down_done", "down_everywhere", "norm_done", "x_digits_written", "producer_waits_for_routing",
                    "producer_has_routing", "producer_layer_issued", "x_digits_visible", "mma_gate_up_start", "mma_gate_up_end",
-                   "mma_down_start", "mma_down_end", "scales_gate_up_end", "scales_down_end", "rows_sent", "norm_reduced")
+                   "mma_down_start", "mma_down_end", "scales_gate_up_end", "scales_down_end", "rows_sent", "norm_reduced",
+                   "cycles_waited_router", "cycles_waited_shared_gate_up", "cycles_waited_routed_gate_up",
+                   "cycles_waited_shared_down", "cycles_waited_routed_down", "cycles_producer_waited_for_slot", "cycles_busy_shared_gate_up", "cycles_busy_routed_gate_up")
 
     def trace(self) -> torch.Tensor:
         """Phase stamps of the last decode run with INKLING_STACK_TRACE=1: int64
-        [n_layers, 256, 24] nanoseconds (zero where a block did not stamp). Synchronises."""
+        [n_layers, 256, 32]: nanosecond stamps in slots 0..23 (zero where a block did not stamp), SM clock
+        cycles spent waiting or holding tiles in slots 24..31 (see TRACE_SLOTS). Synchronises."""
         offset = _abi.lib().ink_moe_stack_trace_offset(self.n_layers, self.hidden, self.intermediate, self.experts,
                                                        self.n_shared, self.top_k)
-        raw = self.scratch[offset:offset + self.n_layers * 256 * 24 * 8].clone()
-        return raw.view(torch.int64).view(self.n_layers, 256, 24).cpu()
+        raw = self.scratch[offset:offset + self.n_layers * 256 * 32 * 8].clone()
+        return raw.view(torch.int64).view(self.n_layers, 256, 32).cpu()
