@@ -243,7 +243,10 @@ __device__ __forceinline__ TilePlan make_plan(const StackArgs& a, bool tc) {
   const int groups = D / S::RT;
   p.g0 = (int)(b * groups / G);
   p.n_g = (int)((b + 1) * groups / G) - p.g0;
-  const int pad_r = (p.n_r + kSC - 1) / kSC * kSC;
+  // The router section is padded to whole rounds of the consumers only where the tensor-core units need their
+  // even slots: empty tiles at the head of a layer take ring slots that could hold the next layer's first
+  // weights while the rows are handed over.
+  const int pad_r = tc ? (p.n_r + kSC - 1) / kSC * kSC : p.n_r;
   p.n_sg = (p.n_u + kSC - 1) / kSC * kSC * S::SG_SPLIT;
   p.n_sd = p.n_sd_real = a.n_shared * p.n_g * S::SD_PER_GROUP;
   p.n_gt = (p.n_g + S::QD_PAIR - 1) / S::QD_PAIR;
@@ -1314,11 +1317,12 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
     const int cw = warp - 1, ct = threadIdx.x - 32;
     constexpr int VG = VecShape<D>::VG, VT = VecShape<D>::VT;   // groups of eight elements per thread, threads that hold some
     const bool holder = ct < VT;
-    long long base = 0;   // index of this layer's first tile in the block's whole sequence
 
-    // first tile index >= start that belongs to this consumer (tile t belongs to consumer t % kSC)
     long long waited = 0;   // (tracing) cycles this warp waited for tiles since the last section stamp
     long long busy = 0, tile_from = 0;   // (tracing) cycles between a tile's arrival and its release
+    long long base = 0;   // index of this layer's first tile in the block's whole sequence
+    // first tile index >= start that belongs to this consumer (tile t belongs to consumer t % kSC; a layer is a
+    // whole number of rounds, so a ring slot always comes back to the same warp)
     auto first_of = [&](int start) -> int { return start + (cw - start % kSC + kSC) % kSC; };
     auto take = [&](int t, const unsigned char*& src, int& slot) -> bool {
       const long long i = base + t;
@@ -1474,7 +1478,7 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
           if (!take(t, src, slot)) break;
           const int i = t - plan.s_sg;
           const int h = (i / kSC) % S::SG_SPLIT, blk = i / (kSC * S::SG_SPLIT);
-          const int unit = blk * kSC + cw;
+          const int unit = blk * kSC + i % kSC;
           if (unit < plan.n_u) {
             if (h == 0) {
 #pragma unroll
