@@ -282,7 +282,9 @@ int ink_moe_stack_encode_banks(void* out_host_512, const void* gate_up_codes, ui
 /* Tracing (the reference's counterpart is utils/profiling.py:36-78): with the environment
  * variable INKLING_STACK_TRACE=1 every block stamps its phase boundaries with the global
  * nanosecond timer into the scratch at this byte offset, laid out
- * [n_layers][256 blocks][24 slots] of uint64 (slot meanings: enum TraceSlot in moe_stack.cu). */
+ * [n_layers][256 blocks][32 slots] of uint64 (slot meanings: enum TraceSlot in moe_stack.cu;
+ * slots 0..23 are stamps, slots 24..31 SM clock cycles that consumer warp 0 waited for tiles or held
+ * them in each section of the layer, and that producer lane 0 waited for its ring slot). */
 size_t ink_moe_stack_trace_offset(int n_layers, int hidden, int intermediate, int experts, int n_shared,
                                   int top_k);
 size_t ink_moe_stack_scratch_bytes(int n_layers, int hidden, int intermediate, int experts, int n_shared,

@@ -130,3 +130,25 @@ def test_replay_equals_eager_under_the_reference_capture_sequence(ib, device, pl
         torch.cuda.synchronize()
         assert torch.equal(replayed, eager)
     model.layers[0].mlp.experts.check_status()
+
+
+def test_banks_packed_by_the_loader_take_the_block_scaled_kernel(ib, device):
+    """The rank's records under the reference's naming -> `pack_resident_experts` -> `apply_resident_plan`: the banks of
+    one kind sit in one allocation, so the grouped path gets its TMA descriptors (tcgen05 block-scaled kernel) and the
+    block still returns what the untouched block returns."""
+    from inkling_b200.loader import pack_resident_experts
+
+    c, p, banks, x, model, kind = _build(device)
+    records = {f"{NAME}.{name}/{e}": tensor for e, bank in banks.items() for name, tensor in bank.items()}
+    state = pack_resident_experts(records, device)
+    swapped = copy.deepcopy(model)
+    ib.apply_resident_plan(swapped, None, state)
+    experts = swapped.layers[0].mlp.experts
+    assert isinstance(experts, ib.ResidentExperts) and experts.bank_maps is not None
+    with torch.inference_mode():
+        for tokens in (1, 12):
+            xs = x[:tokens].to(device).unsqueeze(0)
+            want, got = model(xs), swapped(xs)
+            torch.cuda.synchronize()
+            assert max_rel(got[0].float(), want[0].float()) <= TOL, (kind, tokens)
+    experts.check_status()
