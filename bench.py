@@ -320,6 +320,32 @@ def run_ours(args) -> None:
         "add_rmsnorm": time_graph(lambda layer: ib.kernels.add_rmsnorm(
             layer.partial[:1], stack.residual[:1], stack.norm_weight, stack.eps, stack.normed[:1])),
     }
+    # ---- A/B of the collective, outside the timed region, same blocks and inputs, every rank takes part: the
+    # stated baseline is the reference's shape of the block (my_inkling/offloaded_experts.py:310: separate launches
+    # and ONE NCCL all-reduce of the partial per block), captured in a graph like the one-launch kernel
+    nccl_ms = None
+    if world > 1:
+        plain = ib.MoEStack(list(stack.layers), HIDDEN)
+        plain.one_launch = False
+        for layer in stack.layers:
+            layer.separate_launches = True
+        plain_runner = ib.DecodeStackGraph(plain, dev_x[0], capture=not args.no_graph)
+        for i in range(3):
+            plain_runner.token_in.copy_(dev_x[i % n_inputs])
+            plain_runner.replay()
+        barrier()
+        ab_steps = min(args.steps, 10)
+        start.record()
+        for i in range(ab_steps):
+            plain_runner.token_in.copy_(dev_x[(args.warmup + i) % n_inputs])
+            plain_runner.replay()
+        stop.record()
+        barrier()
+        t = torch.tensor([start.elapsed_time(stop)], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        nccl_ms = float(t.item()) / ab_steps
+        for layer in stack.layers:
+            layer.separate_launches = False
     barrier()
     if rank != 0:
         leave(world)
@@ -366,6 +392,12 @@ def run_ours(args) -> None:
     if layers != args.layers:
         line["config"]["workload"] += f" (only {layers} blocks fit in free device memory)"
         line["config"]["layers"] = layers
+    if nccl_ms is not None:
+        line["collective_ab"] = {
+            "in_kernel_tagged_stores_ms_per_step": launch_ms,
+            "launch_by_launch_nccl_all_reduce_ms_per_step": nccl_ms,
+            "speedup": nccl_ms / launch_ms,
+            "note": "same blocks, graph replay; baseline = 4 launches + one ncclAllReduce per block"}
     if world == 1:
         # configs[3] on four blocks of the same stack (outside the timed region): the grouped tensor-core path
         # against the per-route GEMV at 64 tokens

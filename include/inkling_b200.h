@@ -184,6 +184,29 @@ int ink_add_rmsnorm(const float* partial, void* residual, const void* weight, fl
 int ink_short_conv(const void* x, int x_is_fp32, const float* taps, float* history, const void* residual,
                    void* y, int batch, int hidden, int kernel_size, ink_stream_t stream);
 
+/* Decode attention with the learned relative-position bias, one query token per sequence: the static_decode
+ * branch of MyInklingAttention.forward (my_inkling/model.py:533-612) from the normed query to the output of
+ * scaled_dot_product_attention, with MyInklingRelativeLogits (my_inkling/model.py:112-133) and
+ * MyInklingCache.decode_distance (my_inkling/cache.py:213-228) inside:
+ *   distance[s] = position - s, in a sliding layer (window > 0) modulo the window (the cache is a ring)
+ *   bias[s]     = bf16(r . proj[:, distance]) for 0 <= distance < rel_extent, else 0
+ *   allowed[s]  = 0 <= distance <= position - pad_counts[b]
+ *   full layers with n_floor > 0: tau = 1 + alpha * log(max((position + 1) / n_floor, 1)); q and bias times tau
+ *   out = softmax(scale * q . K^T + bias, over the allowed slots) . V            (FP32 inside, BF16 out)
+ *  q BF16 [batch, heads, head_dim] (after q_norm), r BF16 [batch, heads, d_rel], proj BF16 [d_rel, rel_extent],
+ *  k_cache / v_cache BF16 [batch, kv_heads, slots, head_dim] with the current token already stored
+ *  (ink_update_kv), position: device int64 scalar = tokens stored before this one (a CUDA graph advances it),
+ *  pad_counts int64 [batch] or NULL, out BF16 [batch, heads, head_dim]. head_dim even and a divisor of 512;
+ *  slots + rel_extent <= ~50 000 (the scores live in shared memory). */
+int ink_decode_attention(const void* q, const void* r, const void* proj, const void* k_cache, const void* v_cache,
+                         const int64_t* position, const int64_t* pad_counts, void* out, int batch, int heads,
+                         int kv_heads, int head_dim, int d_rel, int rel_extent, int slots, int window, int n_floor,
+                         float alpha, float scale, ink_stream_t stream);
+/* The decode step of update_kv (kernels/decode.py:149-230): the new token's key and value, BF16
+ * [batch, kv_heads, head_dim], into slot `position` (modulo the window in a sliding layer) of both caches. */
+int ink_update_kv(const void* new_k, const void* new_v, void* k_cache, void* v_cache, const int64_t* position,
+                  int batch, int kv_heads, int head_dim, int slots, int window, ink_stream_t stream);
+
 /* ------------------------------------------------------ grouped projections ------
  * Replace the Triton kernels expert_gemm (kernels/grouped_experts.py:26-148) and
  * expert_reduce (:152-186) for more than a handful of tokens, on the tcgen05 tensor cores.

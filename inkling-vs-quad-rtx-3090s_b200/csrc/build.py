@@ -16,7 +16,7 @@ from pathlib import Path
 CSRC = Path(__file__).resolve().parent
 PACKAGE = CSRC.parent
 LIBRARY = PACKAGE / "libinkling_b200.so"
-SOURCES = ("router_plan.cu", "routed_decode.cu", "stream_decode.cu", "moe_stack.cu", "grouped_experts.cu", "grouped_tc.cu", "glue.cu")
+SOURCES = ("router_plan.cu", "routed_decode.cu", "stream_decode.cu", "moe_stack.cu", "grouped_experts.cu", "grouped_tc.cu", "glue.cu", "attention.cu")
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xptxas=-v",

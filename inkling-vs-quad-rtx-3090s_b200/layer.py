@@ -190,6 +190,10 @@ class FusedMoE(nn.Module):
     sliced on the FFN width. forward(hidden [bs, s, d]) -> [bs, s, d] in the input dtype.
     """
 
+    # True: one token also takes the separate launches (router + plan, gate/up, down) and the NCCL all-reduce,
+    # the shape of the reference's block (my_inkling/offloaded_experts.py:298-314); used as the baseline of A/B runs
+    separate_launches = False
+
     def __init__(self, router_weight, router_bias, global_scale, route_scale: float, top_k: int,
                  shared_gate, shared_up, shared_down, experts: ResidentExperts, device_mesh=None):
         super().__init__()
@@ -265,7 +269,7 @@ class FusedMoE(nn.Module):
         t = flat.shape[0]
         self._reserve(t)
         ex = self.experts
-        if t == 1 and self.one_launch_supported():
+        if t == 1 and self.one_launch_supported() and not self.separate_launches:
             if self._fused is None:
                 # across ranks the kernel delivers and sums the partials itself: no separate collective
                 self._fused = StackDescriptor([self.block_descriptor()], ex.hidden_dim, ex.intermediate_dim,

@@ -1,0 +1,109 @@
+"""Fixtures for decode attention, produced by RUNNING the reference's own modules on the CPU.
+
+    python tests/golden/make_attention_golden.py <reference_root>     (or INKLING_REFERENCE_ROOT)
+
+`MyInklingAttention` (my_inkling/model.py:431-622) with a `MyInklingCache` (my_inkling/cache.py) is prefilled
+with a short prompt, frozen for decode and stepped token by token, once for a sliding-window layer (the ring
+wraps during the run) and once for a full-attention layer with the logarithmic scaling on. Its Triton kernels
+(`update_kv`, `short_conv`) run under TRITON_INTERPRET=1. At chosen steps the inputs of the attention core are
+recorded with hooks -- the normed queries, the relative states, the caches as `scaled_dot_product_attention`
+sees them, the position counter -- together with what `scaled_dot_product_attention` returned and what
+`update_kv` was given. Writes tests/golden/attention.npz (BF16 tensors as their uint16 bit patterns).
+"""
+from __future__ import annotations
+
+import os
+import sys
+from pathlib import Path
+
+os.environ["TRITON_INTERPRET"] = "1"
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+HERE = Path(__file__).resolve().parent
+sys.path.insert(0, str(HERE))
+import attention_cases as ac  # noqa: E402
+
+REFERENCE = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("INKLING_REFERENCE_ROOT")
+if not REFERENCE:
+    raise SystemExit("usage: make_attention_golden.py <reference_root>")
+sys.path.insert(0, REFERENCE)
+from my_inkling import model as ref_model  # noqa: E402  (reference)
+from my_inkling.cache import MyInklingCache  # noqa: E402  (reference)
+
+out: dict[str, np.ndarray] = {}
+
+
+def put(key: str, t: torch.Tensor) -> None:
+    t = t.detach().cpu().contiguous()
+    out[key] = t.view(torch.uint16).numpy() if t.dtype == torch.bfloat16 else t.numpy()
+
+
+def run(kind: str) -> None:
+    c = ac.CASES[kind]
+    config = ref_model.InklingTextConfig(
+        hidden_size=c["hidden"], vocab_size=64, num_hidden_layers=2, pad_token_id=0,
+        layer_types=["hybrid_sliding", "hybrid"], num_attention_heads=c["heads"], num_key_value_heads=c["kv_heads"],
+        head_dim=c["head_dim"], swa_num_attention_heads=c["heads"], swa_num_key_value_heads=c["kv_heads"],
+        swa_head_dim=c["head_dim"], sliding_window_size=c["window"] or 32, d_rel=c["d_rel"], rel_extent=c["rel_extent"],
+        log_scaling_n_floor=c["n_floor"], log_scaling_alpha=c["alpha"])
+    layer_idx = 0 if c["window"] else 1
+    gen = torch.Generator().manual_seed(c["seed"])
+    attn = ref_model.MyInklingAttention(config, layer_idx)
+    for p in attn.parameters():
+        p.data.copy_(torch.randn(p.shape, generator=gen) * c["std"])
+    attn = attn.bfloat16().eval()
+    attn.k_sconv.conv1d.float()   # the reference keeps the convolution taps in FP32
+    attn.v_sconv.conv1d.float()
+    attn.fuse_projections()
+    put(f"{kind}/proj", attn.rel_logits_proj.proj)
+    cache = MyInklingCache(config, batch_size=c["batch"], capacity=c["capacity"], pad_counts=torch.tensor(c["pad_counts"]),
+                           dtype=torch.bfloat16, device="cpu")
+    rec: dict[str, torch.Tensor] = {}
+    attn.q_norm.register_forward_hook(lambda m, i, o: rec.__setitem__("q", o.detach().clone()))
+    attn.qkvr_proj.register_forward_hook(lambda m, i, o: rec.__setitem__("qkvr", o.detach().clone()))
+    original_sdpa, original_update = F.scaled_dot_product_attention, cache.update_attn_cache
+
+    def sdpa(q, k, v, attn_mask=None, **kw):
+        result = original_sdpa(q, k, v, attn_mask=attn_mask, **kw)
+        rec.update(k=k.detach().clone(), v=v.detach().clone(), out=result.detach().clone())
+        return result
+
+    def update(key_states, value_states, layer):
+        rec.update(new_k=key_states.detach().clone(), new_v=value_states.detach().clone())
+        return original_update(key_states, value_states, layer)
+
+    ref_model.F.scaled_dot_product_attention = sdpa
+    cache.update_attn_cache = update
+    with torch.no_grad():
+        attn(torch.randn(c["batch"], c["prompt"], c["hidden"], generator=gen).bfloat16(), cache=cache)
+        cache.advance(c["prompt"])
+        cache.prepare_decode()
+        for step in range(max(c["record"]) + 1):
+            position = int(cache.position)
+            attn(torch.randn(c["batch"], 1, c["hidden"], generator=gen).bfloat16(), cache=cache)
+            if step in c["record"]:
+                r = rec["qkvr"].split(attn.projection_sizes, dim=-1)[3].view(c["batch"], c["heads"], c["d_rel"])
+                put(f"{kind}/{step}/position", torch.tensor(position))
+                put(f"{kind}/{step}/q", rec["q"][:, :, 0])                 # [bs, h, c] after q_norm
+                put(f"{kind}/{step}/r", r)                                  # [bs, h, d_rel]
+                put(f"{kind}/{step}/k_cache", rec["k"])                     # [bs, hk, capacity, c], this token stored
+                put(f"{kind}/{step}/v_cache", rec["v"])
+                put(f"{kind}/{step}/new_k", rec["new_k"][:, :, 0])          # [bs, hk, c] what update_kv stored
+                put(f"{kind}/{step}/new_v", rec["new_v"][:, :, 0])
+                put(f"{kind}/{step}/out", rec["out"][:, :, 0])              # [bs, h, c]
+            cache.advance(1)
+    ref_model.F.scaled_dot_product_attention = original_sdpa
+
+
+def main() -> None:
+    for kind in ac.CASES:
+        run(kind)
+    np.savez_compressed(HERE / "attention.npz", **out)
+    print(f"wrote {len(out)} arrays, {sum(a.nbytes for a in out.values()) / 1e6:.2f} MB raw")
+
+
+if __name__ == "__main__":
+    main()

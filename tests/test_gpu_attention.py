@@ -1,0 +1,83 @@
+"""Decode attention and the cache update through the C ABI against the oracle and against what the reference's
+own modules produced (tests/golden/attention.npz)."""
+import pytest
+import torch
+
+import attention_cases as ac
+from oracle import attention as oa
+from test_attention_oracle import CASES, load
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-2   # of the largest output magnitude: BF16 results of a softmax-weighted sum, FP32 inside
+
+
+@pytest.fixture(scope="module")
+def ib():
+    import inkling_b200
+
+    return inkling_b200
+
+
+def _run(ib, c, f, device, position=None):
+    position = f["position"] if position is None else position
+    pos = torch.tensor(position, dtype=torch.int64, device=device)
+    pad = torch.tensor(c["pad_counts"], dtype=torch.int64, device=device)
+    return ib.kernels.decode_attention(
+        f["q"].to(device).unsqueeze(2), f["r"].to(device).unsqueeze(1), f["proj"].to(device), f["k_cache"].to(device),
+        f["v_cache"].to(device), pos, pad, window=c["window"], log_scaling_n_floor=c["n_floor"],
+        log_scaling_alpha=c["alpha"], scale=ac.SCALE)
+
+
+@pytest.mark.parametrize("kind,step", CASES)
+def test_decode_attention_matches_the_reference_module_and_the_oracle(ib, kind, step):
+    device = torch.device("cuda", 0)
+    c, f = ac.CASES[kind], load(kind, step)
+    got = _run(ib, c, f, device)
+    torch.cuda.synchronize()
+    assert got.shape == (c["batch"], c["heads"], 1, c["head_dim"]) and got.dtype == torch.bfloat16
+    got = got[:, :, 0].float().cpu()
+    want = f["out"].float()
+    exact = oa.decode_attention(f["q"], f["r"], f["proj"], f["k_cache"], f["v_cache"], f["position"],
+                                torch.tensor(c["pad_counts"]), c["window"], c["n_floor"], c["alpha"], ac.SCALE, exact=True).float()
+    assert (got - want).abs().max() <= TOL * want.abs().max()
+    assert (got - exact).abs().max() <= TOL * exact.abs().max()
+
+
+@pytest.mark.parametrize("kind,step", CASES[:1] + CASES[-1:])
+def test_update_kv_stores_the_token_where_the_reference_does(ib, kind, step):
+    device = torch.device("cuda", 0)
+    c, f = ac.CASES[kind], load(kind, step)
+    slot = f["position"] % c["window"] if c["window"] else f["position"]
+    k, v = f["k_cache"].clone(), f["v_cache"].clone()
+    k[:, :, slot] = 0
+    v[:, :, slot] = 0
+    k, v = k.to(device), v.to(device)
+    pos = torch.tensor(f["position"], dtype=torch.int64, device=device)
+    # the reference passes transposed views [bs, hk, 1, c] of a [bs, 1, hk * c] projection
+    key = f["new_k"].to(device).reshape(c["batch"], 1, c["kv_heads"], c["head_dim"]).transpose(1, 2)
+    value = f["new_v"].to(device).reshape(c["batch"], 1, c["kv_heads"], c["head_dim"]).transpose(1, 2)
+    ib.kernels.update_kv(key, value, k, v, pos, c["window"])
+    torch.cuda.synchronize()
+    assert torch.equal(k.cpu(), f["k_cache"]) and torch.equal(v.cpu(), f["v_cache"])
+
+
+def test_decode_attention_at_the_model_shapes_against_the_oracle(ib):
+    """64 heads of 128 channels over 16 key/value heads, a full ring of 512 slots, 16 relative patterns: seeded
+    inputs, compared with the float64 oracle; and a full-attention layer of 4 096 slots with the scaling on."""
+    device = torch.device("cuda", 0)
+    gen = torch.Generator().manual_seed(5)
+    for window, slots, hk, extent, position, n_floor in ((512, 512, 16, 512, 1300, None), (0, 4096, 8, 1024, 3000, 1024)):
+        bs, h, c, d_rel = 2, 64, 128, 16
+        q = torch.randn(bs, h, c, generator=gen).bfloat16()
+        r = torch.randn(bs, h, d_rel, generator=gen).bfloat16()
+        proj = (torch.randn(d_rel, extent, generator=gen) * 0.5).bfloat16()
+        k = torch.randn(bs, hk, slots, c, generator=gen).bfloat16()
+        v = torch.randn(bs, hk, slots, c, generator=gen).bfloat16()
+        pad = torch.tensor([0, 7])
+        want = oa.decode_attention(q, r, proj, k, v, position, pad, window, n_floor, 0.1, 1.0 / c, exact=True).float()
+        got = ib.kernels.decode_attention(q.to(device), r.to(device), proj.to(device), k.to(device), v.to(device),
+                                          torch.tensor(position, dtype=torch.int64, device=device), pad.to(device),
+                                          window=window, log_scaling_n_floor=n_floor, log_scaling_alpha=0.1)
+        torch.cuda.synchronize()
+        got = got[:, :, 0].float().cpu()
+        assert (got - want).abs().max() <= TOL * want.abs().max(), (window, float((got - want).abs().max()), float(want.abs().max()))
