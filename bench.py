@@ -548,6 +548,74 @@ def run_batched(args) -> None:
         "by_tokens": numbers}), flush=True)
 
 
+def run_attention(args) -> None:
+    """Decode attention on its own (not the headline metric): one token against the K/V caches of `--layers` layers
+    at the model's shapes (64 heads of 128 channels; sliding layers 16 key/value heads x 512 slots, every sixth layer
+    full attention with 8 key/value heads x 4096 slots), captured in one graph; the caches of all layers together
+    are larger than the L2. Prints one JSON line: microseconds per layer and cache bytes per second."""
+    import torch
+
+    import inkling_b200 as ib
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    gen = torch.Generator().manual_seed(3)
+    heads, c, d_rel, batch = 64, 128, 16, 1
+    layers, cache_bytes = [], 0
+    for i in range(args.layers):
+        full = (i + 1) % 6 == 0
+        hk, slots, extent, window = (8, 4096, 1024, 0) if full else (16, 512, 512, 512)
+        k = torch.randn(batch, hk, slots, c, generator=gen).to(torch.bfloat16).to(device)
+        v = torch.randn(batch, hk, slots, c, generator=gen).to(torch.bfloat16).to(device)
+        proj = (torch.randn(d_rel, extent, generator=gen) * 0.5).to(torch.bfloat16).to(device)
+        layers.append((k, v, proj, window, 1024 if full else None))
+        cache_bytes += 2 * 2 * batch * hk * c * (slots if window else 3001)   # K and V rows of the slots in use
+    q = torch.randn(batch, heads, c, generator=gen).to(torch.bfloat16).to(device)
+    r = torch.randn(batch, heads, d_rel, generator=gen).to(torch.bfloat16).to(device)
+    new = torch.randn(batch, 16, 1, c, generator=gen).to(torch.bfloat16).to(device)
+    # every slot of a sliding ring is in use; a full layer has seen 3000 of its 4096 positions
+    pos_sliding = torch.tensor(5000, dtype=torch.int64, device=device)
+    pos_full = torch.tensor(3000, dtype=torch.int64, device=device)
+    out = torch.empty(batch, heads, 1, c, dtype=torch.bfloat16, device=device)
+
+    def step():
+        for k, v, proj, window, n_floor in layers:
+            position = pos_sliding if window else pos_full
+            ib.kernels.update_kv(new[:, : k.shape[1]], new[:, : k.shape[1]], k, v, position, window)
+            ib.kernels.decode_attention(q, r, proj, k, v, position, None, window=window, log_scaling_n_floor=n_floor, out=out)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        step()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(args.warmup):
+        graph.replay()
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(args.steps):
+        graph.replay()
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop) / args.steps
+    peaks, peak_kind = load_peaks()
+    gbs = cache_bytes / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "decode_attention_layer_us", "value": ms * 1e3 / args.layers, "unit": "us", "higher_is_better": False,
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "data": "synthetic",
+        "config": {"workload": f"decode attention + cache update of {args.layers} layers, 1 token, 64 heads x 128, sliding 16 x 512 "
+                               "slots, every sixth layer full 8 x 4096 slots; graph replay", "cache_bytes_per_step": cache_bytes},
+        "gpu_launches": 2 * args.layers * args.steps,
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "peak_kind": peak_kind, "unit": "GB/s",
+                     "frac": gbs / peaks["hbm_gbs"], "traffic": None}}), flush=True)
+
+
 def leave(world: int) -> None:
     """Multi-rank runs end here, after the last barrier: tearing an NCCL communicator down while
     captured graphs still hold its kernels can block for minutes, so the ranks flush and exit."""
@@ -568,8 +636,12 @@ def main() -> None:
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--batched", action="store_true", help="configs[3] instead of the headline workload")
     parser.add_argument("--batched-blocks", type=int, default=4, help="blocks rotated by --batched (1 for a profiler capture)")
+    parser.add_argument("--attention", action="store_true", help="decode attention on its own instead of the headline workload")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.attention:
+        run_attention(args)
+        return
     if args.batched:
         run_batched(args)
     elif args.impl == "reference":

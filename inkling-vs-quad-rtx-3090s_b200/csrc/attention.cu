@@ -9,6 +9,9 @@ namespace ink {
 
 constexpr int kAttnThreads = 256;
 constexpr int kAttnWarps = kAttnThreads / 32;
+constexpr int kAttnKeys = 8;                                // cache slots a warp scores side by side
+constexpr int kAttnSlots = kAttnWarps * kAttnKeys;          // slots per block: 64
+constexpr int kAttnPartial = 2;                             // floats in front of a partial result: running maximum, sum
 
 struct AttnArgs {
   const uint16_t* q;        // [bs, h, c] after q_norm
@@ -18,127 +21,187 @@ struct AttnArgs {
   const uint16_t* v;
   const int64_t* position;  // device scalar: tokens stored before this one
   const int64_t* pad_counts;   // [bs] or null
+  float* partial;           // [bs, h, splits, 2 + c]: maximum, sum of exponentials, unnormalised weighted values
   uint16_t* out;            // [bs, h, c]
-  int heads, kv_heads, c, d_rel, extent, slots, window, n_floor;
+  int heads, kv_heads, c, d_rel, extent, slots, window, n_floor, splits;
   float alpha, scale;
 };
 
-__device__ __forceinline__ float block_max(float v, float* red) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  if (lane == 0) red[warp] = v;
-  __syncthreads();
-  float m = red[0];
-#pragma unroll
-  for (int w = 1; w < kAttnWarps; ++w) m = fmaxf(m, red[w]);
-  __syncthreads();
-  return m;
-}
-__device__ __forceinline__ float block_sum(float v, float* red) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  v = warp_sum(v);
-  if (lane == 0) red[warp] = v;
-  __syncthreads();
-  float s = 0.f;
-#pragma unroll
-  for (int w = 0; w < kAttnWarps; ++w) s += red[w];
-  __syncthreads();
-  return s;
-}
-
-// Shared memory: q [c] | logits [extent] | scores [slots] | partial sums [kAttnThreads * 2]
+// One block per (head, sequence, group of 64 cache slots). A decode step has few (head, sequence) pairs and every
+// load is a trip to DRAM, so the work is cut along the cache (as in split-K / flash decoding) and every block asks
+// for ALL it needs at once: its key rows, its value rows (which slots are allowed is known before any score),
+// the query and the relative states. It leaves a partial softmax (maximum, sum, weighted values) that
+// attention_combine_kernel joins.
+template <int C>
 __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(AttnArgs a) {
-  extern __shared__ __align__(16) float smem[];
-  __shared__ float s_red[kAttnWarps];
-  float* s_q = smem;
-  float* s_logits = s_q + a.c;
-  float* s_scores = s_logits + a.extent;
-  float* s_part = s_scores + a.slots;
-  const int head = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  constexpr int kWords = C / 2;                          // 32-bit words of a row = channel pairs
+  constexpr int kPerLane = (kWords + 31) / 32;           // words of a key row per lane
+  constexpr int kParts = kAttnThreads / kWords;          // threads per channel pair in the value pass
+  constexpr int kValues = kAttnSlots / kParts;           // value rows per thread
+  static_assert(kAttnThreads % kWords == 0 && kAttnSlots % kParts == 0, "head_dim does not tile the block");
+  __shared__ float s_q[C];
+  __shared__ float s_bias[kAttnSlots];
+  __shared__ float s_scores[kAttnSlots];
+  __shared__ float s_part[kAttnThreads * 2];
+  const int head = blockIdx.x, b = blockIdx.y, split = blockIdx.z, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int kv_head = head / (a.heads / a.kv_heads);
-  const long long position = *a.position;
-  const long long pad = a.pad_counts ? a.pad_counts[b] : 0;
+  const int slot_base = split * kAttnSlots;
+  // positions fit 32 bits; the ring arithmetic is done once per block (position modulo the window), not per slot
+  const int position = (int)*a.position;
+  const int reach = position - (int)(a.pad_counts ? a.pad_counts[b] : 0);   // largest distance that is not padding
+  const int ring_position = a.window ? position % a.window : 0;
+  auto distance_of = [&](int slot) -> int {
+    if (!a.window) return position - slot;
+    const int d = ring_position - (slot < a.window ? slot : slot % a.window);
+    return d < 0 ? d + a.window : d;
+  };
+  auto allowed_at = [&](int slot) -> bool {
+    const int d = distance_of(slot);
+    return slot < a.slots && d >= 0 && d <= reach;
+  };
+  // ---- everything from memory, in flight together
+  const uint16_t* keys = a.k + ((size_t)b * a.kv_heads + kv_head) * a.slots * C;
+  const uint16_t* values = a.v + ((size_t)b * a.kv_heads + kv_head) * a.slots * C;
+  bool k_allowed[kAttnKeys];
+  uint32_t kw[kAttnKeys][kPerLane];
+#pragma unroll
+  for (int j = 0; j < kAttnKeys; ++j) {
+    const int slot = slot_base + warp * kAttnKeys + j;
+    k_allowed[j] = allowed_at(slot);
+    const uint32_t* row = reinterpret_cast<const uint32_t*>(keys + (size_t)slot * C);
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) kw[j][i] = (k_allowed[j] && i * 32 + lane < kWords) ? __ldg(row + i * 32 + lane) : 0u;
+  }
+  const int pair = tid % kWords, part = tid / kWords;   // value pass: this thread's channel pair, its slots part, part + kParts, ...
+  uint32_t vw[kValues];
+#pragma unroll
+  for (int n = 0; n < kValues; ++n) {
+    const int slot = slot_base + part + n * kParts;
+    // (a slot that is not allowed may hold anything: it is not read)
+    vw[n] = allowed_at(slot) ? __ldg(reinterpret_cast<const uint32_t*>(values + (size_t)slot * C) + pair) : 0u;
+  }
   // logarithmic scaling of full-attention layers: query and bias times tau, each rounded to BF16 (the reference
   // multiplies in FP32 and casts back, my_inkling/model.py:583-590)
   const bool scaled = a.window == 0 && a.n_floor > 0;
   float tau = 1.f;
   if (scaled) tau = 1.f + a.alpha * logf(fmaxf((float)(position + 1) / (float)a.n_floor, 1.f));
-  const uint16_t* q = a.q + ((size_t)b * a.heads + head) * a.c;
-  for (int i = tid; i < a.c; i += kAttnThreads) {
-    const float x = bf16_to_f32(q[i]);
-    s_q[i] = scaled ? round_bf16(x * tau) : x;
+  if (tid < C) {
+    const float x = bf16_to_f32(a.q[((size_t)b * a.heads + head) * C + tid]);
+    s_q[tid] = scaled ? round_bf16(x * tau) : x;
   }
-  // relative logits of this head: r @ proj, a BF16 matmul (FP32 sum, rounded once)
-  const uint16_t* r = a.r + ((size_t)b * a.heads + head) * a.d_rel;
-  for (int e = tid; e < a.extent; e += kAttnThreads) {
-    float sum = 0.f;
-    for (int j = 0; j < a.d_rel; ++j) sum = fmaf(bf16_to_f32(r[j]), bf16_to_f32(a.proj[(size_t)j * a.extent + e]), sum);
-    s_logits[e] = round_bf16(sum);
-  }
-  __syncthreads();
-  // scores: one warp per cache slot
-  const uint16_t* keys = a.k + ((size_t)b * a.kv_heads + kv_head) * a.slots * a.c;
-  float local_max = -INFINITY;
-  for (int slot = warp; slot < a.slots; slot += kAttnWarps) {
-    long long distance = position - slot;
-    if (a.window) distance = ((distance % a.window) + a.window) % a.window;
-    const bool allowed = distance >= 0 && distance <= position - pad;
-    float score = -INFINITY;
-    if (allowed) {
-      const uint32_t* row = reinterpret_cast<const uint32_t*>(keys + (size_t)slot * a.c);
-      float dot = 0.f;
-      for (int i = lane; i < a.c / 2; i += 32) {
-        const uint32_t w = __ldg(row + i);
-        dot = fmaf(s_q[2 * i], bf16lo(w), dot);
-        dot = fmaf(s_q[2 * i + 1], bf16hi(w), dot);
-      }
-      dot = warp_sum(dot);
-      float bias = distance < a.extent ? s_logits[distance] : 0.f;
+  // relative bias of this block's slots: (r @ proj)[distance], a BF16 matmul (FP32 sum, rounded once)
+  if (tid >= kAttnThreads - kAttnSlots) {
+    const int i = tid - (kAttnThreads - kAttnSlots), slot = slot_base + i;
+    const int d = distance_of(slot);
+    float bias = 0.f;
+    if (slot < a.slots && d >= 0 && d < a.extent) {
+      const uint16_t* r = a.r + ((size_t)b * a.heads + head) * a.d_rel;
+      float sum = 0.f;
+#pragma unroll 8
+      for (int j = 0; j < a.d_rel; ++j) sum = fmaf(bf16_to_f32(r[j]), bf16_to_f32(__ldg(a.proj + (size_t)j * a.extent + d)), sum);
+      bias = round_bf16(sum);
       if (scaled) bias = round_bf16(bias * tau);
-      score = dot * a.scale + bias;
     }
-    if (lane == 0) s_scores[slot] = score;
-    local_max = fmaxf(local_max, score);
+    s_bias[i] = bias;
   }
   __syncthreads();
-  const float top = block_max(local_max, s_red);
-  float local_sum = 0.f;
-  for (int slot = tid; slot < a.slots; slot += kAttnThreads) {
-    const float s = s_scores[slot];
-    const float p = s == -INFINITY ? 0.f : __expf(s - top);
-    s_scores[slot] = p;
-    local_sum += p;
-  }
-  const float total = block_sum(local_sum, s_red);   // (its barriers also publish the weights)
-  // weighted sum of the values: a thread owns a pair of channels and every `parts`-th slot
-  const int pairs = a.c / 2, parts = kAttnThreads / pairs;
-  const int pair = tid % pairs, part = tid / pairs;
-  float acc0 = 0.f, acc1 = 0.f;
-  if (part < parts) {
-    const uint16_t* values = a.v + ((size_t)b * a.kv_heads + kv_head) * a.slots * a.c;
-    for (int slot = part; slot < a.slots; slot += parts) {
-      const float p = s_scores[slot];
-      if (p != 0.f) {
-        const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(values + (size_t)slot * a.c) + pair);
-        acc0 = fmaf(p, bf16lo(w), acc0);
-        acc1 = fmaf(p, bf16hi(w), acc1);
+  // ---- scores: warp w holds the key rows of the slots w * 8 .. w * 8 + 7 of the block
+  {
+    float dot[kAttnKeys];
+#pragma unroll
+    for (int j = 0; j < kAttnKeys; ++j) {
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < kPerLane; ++i) {
+        const int at = i * 32 + lane;
+        if (at < kWords) {
+          sum = fmaf(s_q[2 * at], bf16lo(kw[j][i]), sum);
+          sum = fmaf(s_q[2 * at + 1], bf16hi(kw[j][i]), sum);
+        }
       }
+      dot[j] = sum;
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+      for (int j = 0; j < kAttnKeys; ++j) dot[j] += __shfl_xor_sync(0xffffffffu, dot[j], o);
+    }
+    if (lane == 0) {
+#pragma unroll
+      for (int j = 0; j < kAttnKeys; ++j)
+        s_scores[warp * kAttnKeys + j] = k_allowed[j] ? dot[j] * a.scale + s_bias[warp * kAttnKeys + j] : -INFINITY;
+    }
+  }
+  __syncthreads();
+  // the block's 64 scores: every warp finds the maximum for itself (two scores per lane, five shuffles), the
+  // first two warps turn the scores into exponentials once for everybody
+  static_assert(kAttnSlots == 64, "two scores per lane");
+  float top = fmaxf(s_scores[lane], s_scores[lane + 32]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
+  if (tid < kAttnSlots) {
+    const float sc = s_scores[tid];
+    s_bias[tid] = (sc == -INFINITY) ? 0.f : __expf(sc - top);   // (the biases are in the scores by now)
+  }
+  __syncthreads();
+  float acc0 = 0.f, acc1 = 0.f, sum = 0.f;
+#pragma unroll
+  for (int n = 0; n < kValues; ++n) {
+    const float p = s_bias[part + n * kParts];
+    acc0 = fmaf(p, bf16lo(vw[n]), acc0);
+    acc1 = fmaf(p, bf16hi(vw[n]), acc1);
+    sum += p;
   }
   s_part[2 * tid] = acc0;
   s_part[2 * tid + 1] = acc1;
   __syncthreads();
-  if (tid < pairs) {
-    float o0 = 0.f, o1 = 0.f;
-    for (int p = 0; p < parts; ++p) {
-      o0 += s_part[2 * (p * pairs + tid)];
-      o1 += s_part[2 * (p * pairs + tid) + 1];
+  if (pair == 0) s_scores[part] = sum;   // (the scores are not needed any more) one partial sum of exponentials per part
+  __syncthreads();
+  if (tid < kWords) {
+    float o0 = 0.f, o1 = 0.f, total = 0.f;
+#pragma unroll
+    for (int p = 0; p < kParts; ++p) {
+      o0 += s_part[2 * (p * kWords + tid)];
+      o1 += s_part[2 * (p * kWords + tid) + 1];
+      total += s_scores[p];
     }
-    const float inv = 1.f / total;
-    uint32_t* out = reinterpret_cast<uint32_t*>(a.out + ((size_t)b * a.heads + head) * a.c);
-    out[tid] = f32_to_bf16_bits(o0 * inv) | (f32_to_bf16_bits(o1 * inv) << 16);
+    if (a.splits == 1) {
+      const float inv = 1.f / total;
+      uint32_t* out = reinterpret_cast<uint32_t*>(a.out + ((size_t)b * a.heads + head) * C);
+      out[tid] = f32_to_bf16_bits(o0 * inv) | (f32_to_bf16_bits(o1 * inv) << 16);
+    } else {
+      float* mine = a.partial + (((size_t)b * a.heads + head) * a.splits + split) * (kAttnPartial + C);
+      if (tid == 0) {
+        mine[0] = top;
+        mine[1] = total;
+      }
+      mine[kAttnPartial + 2 * tid] = o0;
+      mine[kAttnPartial + 2 * tid + 1] = o1;
+    }
   }
+}
+
+// joins the partial softmaxes of one (head, sequence): out = sum_i acc_i e^(m_i - M) / sum_i l_i e^(m_i - M)
+__global__ void attention_combine_kernel(AttnArgs a) {
+  const int head = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+  const float* base = a.partial + ((size_t)b * a.heads + head) * a.splits * (kAttnPartial + a.c);
+  const int stride = kAttnPartial + a.c;
+  float top = -INFINITY;
+  for (int i = 0; i < a.splits; ++i) top = fmaxf(top, base[(size_t)i * stride]);
+  if (tid >= a.c / 2) return;
+  float o0 = 0.f, o1 = 0.f, total = 0.f;
+  for (int i = 0; i < a.splits; ++i) {
+    const float* part = base + (size_t)i * stride;
+    const float m = part[0];
+    if (m == -INFINITY) continue;
+    const float weight = __expf(m - top);
+    total = fmaf(part[1], weight, total);
+    o0 = fmaf(part[kAttnPartial + 2 * tid], weight, o0);
+    o1 = fmaf(part[kAttnPartial + 2 * tid + 1], weight, o1);
+  }
+  const float inv = 1.f / total;
+  uint32_t* out = reinterpret_cast<uint32_t*>(a.out + ((size_t)b * a.heads + head) * a.c);
+  out[tid] = f32_to_bf16_bits(o0 * inv) | (f32_to_bf16_bits(o1 * inv) << 16);
 }
 
 // the new token's key and value into slot `position` (modulo the window in a sliding layer) of both caches
@@ -159,29 +222,43 @@ __global__ void update_kv_kernel(const uint16_t* __restrict__ new_k, const uint1
 
 using namespace ink;
 
+extern "C" size_t ink_decode_attention_workspace_bytes(int batch, int heads, int head_dim, int slots) {
+  const size_t splits = ((size_t)slots + kAttnSlots - 1) / kAttnSlots;
+  return splits <= 1 ? 0 : sizeof(float) * (size_t)batch * heads * splits * (kAttnPartial + head_dim);
+}
+
 extern "C" int ink_decode_attention(const void* q, const void* r, const void* proj, const void* k_cache,
                                     const void* v_cache, const int64_t* position, const int64_t* pad_counts, void* out,
                                     int batch, int heads, int kv_heads, int head_dim, int d_rel, int rel_extent, int slots,
-                                    int window, int n_floor, float alpha, float scale, ink_stream_t stream) {
+                                    int window, int n_floor, float alpha, float scale, void* workspace,
+                                    size_t workspace_bytes, ink_stream_t stream) {
   INK_REQUIRE(q && r && proj && k_cache && v_cache && position && out, kBadArgument, "decode_attention: null pointer argument");
   INK_REQUIRE(batch >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0, kBadArgument,
               "decode_attention: batch=%d heads=%d kv_heads=%d", batch, heads, kv_heads);
-  INK_REQUIRE(head_dim >= 2 && head_dim % 2 == 0 && head_dim <= 2 * kAttnThreads && kAttnThreads % (head_dim / 2) == 0,
-              kUnsupportedShape, "decode_attention: head_dim=%d unsupported (even, a divisor of %d)", head_dim, 2 * kAttnThreads);
+  INK_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256, kUnsupportedShape,
+              "decode_attention: head_dim=%d unsupported (built for 64, 128 and 256)", head_dim);
   INK_REQUIRE(d_rel > 0 && rel_extent > 0 && slots > 0 && window >= 0 && (window == 0 || window <= slots), kBadArgument,
               "decode_attention: d_rel=%d rel_extent=%d slots=%d window=%d", d_rel, rel_extent, slots, window);
-  const size_t smem = sizeof(float) * ((size_t)head_dim + rel_extent + slots + 2 * kAttnThreads);
-  INK_REQUIRE(smem <= 200 * 1024, kUnsupportedShape, "decode_attention: %d slots + %d relative positions do not fit shared memory",
-              slots, rel_extent);
-  INK_REQUIRE(aligned16(q) && aligned16(k_cache) && aligned16(v_cache) && aligned16(out) && (head_dim * 2) % 4 == 0, kMisaligned,
-              "decode_attention: buffers must be 16-byte aligned");
+  const int splits = (slots + kAttnSlots - 1) / kAttnSlots;
+  INK_REQUIRE(splits <= 65535 && batch <= 65535, kUnsupportedShape, "decode_attention: %d slots or %d sequences exceed the grid", slots, batch);
+  const size_t need = ink_decode_attention_workspace_bytes(batch, heads, head_dim, slots);
+  INK_REQUIRE(need == 0 || (workspace && workspace_bytes >= need), kBadArgument,
+              "decode_attention: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+  INK_REQUIRE(aligned16(q) && aligned16(k_cache) && aligned16(v_cache) && aligned16(out) && (need == 0 || aligned16(workspace)),
+              kMisaligned, "decode_attention: buffers must be 16-byte aligned");
   if (batch == 0) return kOk;
   AttnArgs a{(const uint16_t*)q, (const uint16_t*)r, (const uint16_t*)proj, (const uint16_t*)k_cache, (const uint16_t*)v_cache,
-             position, pad_counts, (uint16_t*)out, heads, kv_heads, head_dim, d_rel, rel_extent, slots, window, n_floor, alpha, scale};
-  cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  INK_REQUIRE(e == cudaSuccess, kLaunchFailed, "decode_attention: %s", cudaGetErrorString(e));
-  decode_attention_kernel<<<dim3(heads, batch), kAttnThreads, smem, (cudaStream_t)stream>>>(a);
+             position, pad_counts, (float*)workspace, (uint16_t*)out, heads, kv_heads, head_dim, d_rel, rel_extent, slots, window,
+             n_floor, splits, alpha, scale};
+  const dim3 grid(heads, batch, splits);
+  if (head_dim == 64) decode_attention_kernel<64><<<grid, kAttnThreads, 0, (cudaStream_t)stream>>>(a);
+  else if (head_dim == 128) decode_attention_kernel<128><<<grid, kAttnThreads, 0, (cudaStream_t)stream>>>(a);
+  else decode_attention_kernel<256><<<grid, kAttnThreads, 0, (cudaStream_t)stream>>>(a);
   INK_CHECK_LAUNCH("decode_attention");
+  if (splits > 1) {
+    attention_combine_kernel<<<dim3(heads, batch), 128, 0, (cudaStream_t)stream>>>(a);
+    INK_CHECK_LAUNCH("decode_attention (combine)");
+  }
   return kOk;
 }
 

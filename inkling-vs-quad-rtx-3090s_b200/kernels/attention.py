@@ -10,6 +10,8 @@ import torch
 
 from . import _abi
 
+_workspaces: dict = {}   # (device, bytes) -> buffer for the partial results, reused from call to call (one stream)
+
 
 def update_kv(key, value, k_cache, v_cache, start, window: int = 0) -> None:
     """key, value BF16 [bs, hk, 1, c] (any strides over bs/hk, as the reference's transposed views), caches BF16
@@ -49,10 +51,17 @@ def decode_attention(query, relative_states, proj, k_cache, v_cache, position, p
         assert pad_counts.dtype == torch.int64 and pad_counts.numel() == bs and pad_counts.is_contiguous()
     if out is None:
         out = torch.empty((bs, h, 1, c), dtype=torch.bfloat16, device=q.device)
+    need = _abi.lib().ink_decode_attention_workspace_bytes(bs, h, c, slots)
+    workspace = None
+    if need:
+        key = (q.device, need)
+        workspace = _workspaces.get(key)
+        if workspace is None:
+            workspace = _workspaces[key] = torch.empty(need, dtype=torch.uint8, device=q.device)
     _abi.require_cuda(q, r, proj, k_cache, v_cache, position, pad_counts, out)
     _abi.check(_abi.lib().ink_decode_attention(
         q.data_ptr(), r.data_ptr(), proj.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), position.data_ptr(),
         _abi.ptr(pad_counts), out.data_ptr(), bs, h, hk, c, d_rel, extent, slots, int(window),
         int(log_scaling_n_floor or 0), float(log_scaling_alpha), float(scale if scale is not None else 1.0 / c),
-        _abi.stream()))
+        _abi.ptr(workspace), need, _abi.stream()))
     return out
