@@ -198,8 +198,10 @@ int ink_short_conv(const void* x, int x_is_fp32, const float* taps, float* histo
  *  (ink_update_kv), position: device int64 scalar = tokens stored before this one (a CUDA graph advances it),
  *  pad_counts int64 [batch] or NULL, out BF16 [batch, heads, head_dim]. head_dim 64, 128 or 256.
  *  The cache is cut into groups of 64 slots, one block per (head, sequence, group); with more than
- *  one group the partial results pass through `workspace` (ink_decode_attention_workspace_bytes, 16-byte aligned,
- *  contents irrelevant before the call) and a second kernel joins them. */
+ *  one group the partial results pass through `workspace` (ink_decode_attention_workspace_bytes, 16-byte aligned) and
+ *  the block that stores the last partial of a (sequence, head) joins them. The workspace must be ZERO before its first
+ *  use (it starts with one arrival counter per (sequence, head)); every launch leaves the counters zero again, so the
+ *  same workspace serves call after call on one stream. */
 size_t ink_decode_attention_workspace_bytes(int batch, int heads, int head_dim, int slots);
 int ink_decode_attention(const void* q, const void* r, const void* proj, const void* k_cache, const void* v_cache,
                          const int64_t* position, const int64_t* pad_counts, void* out, int batch, int heads,

@@ -22,6 +22,7 @@ struct AttnArgs {
   const int64_t* position;  // device scalar: tokens stored before this one
   const int64_t* pad_counts;   // [bs] or null
   float* partial;           // [bs, h, splits, 2 + c]: maximum, sum of exponentials, unnormalised weighted values
+  unsigned* arrived;        // [bs, h] blocks of a (sequence, head) that have stored their partial; zero between launches
   uint16_t* out;            // [bs, h, c]
   int heads, kv_heads, c, d_rel, extent, slots, window, n_floor, splits;
   float alpha, scale;
@@ -30,8 +31,8 @@ struct AttnArgs {
 // One block per (head, sequence, group of 64 cache slots). A decode step has few (head, sequence) pairs and every
 // load is a trip to DRAM, so the work is cut along the cache (as in split-K / flash decoding) and every block asks
 // for ALL it needs at once: its key rows, its value rows (which slots are allowed is known before any score),
-// the query and the relative states. It leaves a partial softmax (maximum, sum, weighted values) that
-// attention_combine_kernel joins.
+// the query and the relative states. It leaves a partial softmax (maximum, sum, weighted values); the block that
+// stores the last partial of a (sequence, head) joins them.
 template <int C>
 __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(AttnArgs a) {
   constexpr int kWords = C / 2;                          // 32-bit words of a row = channel pairs
@@ -177,31 +178,56 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(AttnArgs
       }
       mine[kAttnPartial + 2 * tid] = o0;
       mine[kAttnPartial + 2 * tid + 1] = o1;
+      __threadfence();   // every writer pushes its own stores out before the block is counted
     }
   }
-}
-
-// joins the partial softmaxes of one (head, sequence): out = sum_i acc_i e^(m_i - M) / sum_i l_i e^(m_i - M)
-__global__ void attention_combine_kernel(AttnArgs a) {
-  const int head = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
-  const float* base = a.partial + ((size_t)b * a.heads + head) * a.splits * (kAttnPartial + a.c);
-  const int stride = kAttnPartial + a.c;
-  float top = -INFINITY;
-  for (int i = 0; i < a.splits; ++i) top = fmaxf(top, base[(size_t)i * stride]);
-  if (tid >= a.c / 2) return;
-  float o0 = 0.f, o1 = 0.f, total = 0.f;
-  for (int i = 0; i < a.splits; ++i) {
-    const float* part = base + (size_t)i * stride;
-    const float m = part[0];
-    if (m == -INFINITY) continue;
-    const float weight = __expf(m - top);
-    total = fmaf(part[1], weight, total);
-    o0 = fmaf(part[kAttnPartial + 2 * tid], weight, o0);
-    o1 = fmaf(part[kAttnPartial + 2 * tid + 1], weight, o1);
+  if (a.splits == 1) return;
+  // The block that stores the last partial of its (sequence, head) joins them all:
+  //   out = sum_i acc_i e^(m_i - M) / sum_i l_i e^(m_i - M)
+  __shared__ bool s_last;
+  __syncthreads();
+  if (tid == 0) {
+    unsigned* arrived = a.arrived + (size_t)b * a.heads + head;
+    s_last = atomicAdd(arrived, 1u) + 1u == (unsigned)a.splits;
+    if (s_last) *arrived = 0u;   // left as found, for the next launch
   }
-  const float inv = 1.f / total;
-  uint32_t* out = reinterpret_cast<uint32_t*>(a.out + ((size_t)b * a.heads + head) * a.c);
-  out[tid] = f32_to_bf16_bits(o0 * inv) | (f32_to_bf16_bits(o1 * inv) << 16);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const int stride = kAttnPartial + C;
+  const float* base = a.partial + ((size_t)b * a.heads + head) * a.splits * stride;
+  float all_top = -INFINITY;
+  for (int i = lane; i < a.splits; i += 32) all_top = fmaxf(all_top, __ldcg(base + (size_t)i * stride));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) all_top = fmaxf(all_top, __shfl_xor_sync(0xffffffffu, all_top, o));
+  // thread = (channel pair, part): every part takes every kParts-th partial, then the parts are added up
+  float o0 = 0.f, o1 = 0.f, total = 0.f;
+  for (int i = part; i < a.splits; i += kParts) {
+    const float* from = base + (size_t)i * stride;
+    const float m = __ldcg(from);
+    if (m == -INFINITY) continue;
+    const float weight = __expf(m - all_top);
+    total = fmaf(__ldcg(from + 1), weight, total);
+    const float2 acc = __ldcg(reinterpret_cast<const float2*>(from + kAttnPartial) + pair);
+    o0 = fmaf(acc.x, weight, o0);
+    o1 = fmaf(acc.y, weight, o1);
+  }
+  s_part[2 * tid] = o0;
+  s_part[2 * tid + 1] = o1;
+  if (pair == 0) s_scores[part] = total;
+  __syncthreads();
+  if (tid < kWords) {
+    float f0 = 0.f, f1 = 0.f, sum_all = 0.f;
+#pragma unroll
+    for (int p = 0; p < kParts; ++p) {
+      f0 += s_part[2 * (p * kWords + tid)];
+      f1 += s_part[2 * (p * kWords + tid) + 1];
+      sum_all += s_scores[p];
+    }
+    const float inv = 1.f / sum_all;
+    uint32_t* out = reinterpret_cast<uint32_t*>(a.out + ((size_t)b * a.heads + head) * C);
+    out[tid] = f32_to_bf16_bits(f0 * inv) | (f32_to_bf16_bits(f1 * inv) << 16);
+  }
 }
 
 // the new token's key and value into slot `position` (modulo the window in a sliding layer) of both caches
@@ -222,9 +248,11 @@ __global__ void update_kv_kernel(const uint16_t* __restrict__ new_k, const uint1
 
 using namespace ink;
 
+static size_t attention_counter_bytes(int batch, int heads) { return ((size_t)batch * heads * sizeof(unsigned) + 255) / 256 * 256; }
+
 extern "C" size_t ink_decode_attention_workspace_bytes(int batch, int heads, int head_dim, int slots) {
   const size_t splits = ((size_t)slots + kAttnSlots - 1) / kAttnSlots;
-  return splits <= 1 ? 0 : sizeof(float) * (size_t)batch * heads * splits * (kAttnPartial + head_dim);
+  return splits <= 1 ? 0 : attention_counter_bytes(batch, heads) + sizeof(float) * (size_t)batch * heads * splits * (kAttnPartial + head_dim);
 }
 
 extern "C" int ink_decode_attention(const void* q, const void* r, const void* proj, const void* k_cache,
@@ -248,17 +276,13 @@ extern "C" int ink_decode_attention(const void* q, const void* r, const void* pr
               kMisaligned, "decode_attention: buffers must be 16-byte aligned");
   if (batch == 0) return kOk;
   AttnArgs a{(const uint16_t*)q, (const uint16_t*)r, (const uint16_t*)proj, (const uint16_t*)k_cache, (const uint16_t*)v_cache,
-             position, pad_counts, (float*)workspace, (uint16_t*)out, heads, kv_heads, head_dim, d_rel, rel_extent, slots, window,
+             position, pad_counts, (float*)((char*)workspace + attention_counter_bytes(batch, heads)), (unsigned*)workspace, (uint16_t*)out, heads, kv_heads, head_dim, d_rel, rel_extent, slots, window,
              n_floor, splits, alpha, scale};
   const dim3 grid(heads, batch, splits);
   if (head_dim == 64) decode_attention_kernel<64><<<grid, kAttnThreads, 0, (cudaStream_t)stream>>>(a);
   else if (head_dim == 128) decode_attention_kernel<128><<<grid, kAttnThreads, 0, (cudaStream_t)stream>>>(a);
   else decode_attention_kernel<256><<<grid, kAttnThreads, 0, (cudaStream_t)stream>>>(a);
   INK_CHECK_LAUNCH("decode_attention");
-  if (splits > 1) {
-    attention_combine_kernel<<<dim3(heads, batch), 128, 0, (cudaStream_t)stream>>>(a);
-    INK_CHECK_LAUNCH("decode_attention (combine)");
-  }
   return kOk;
 }
 

@@ -57,7 +57,7 @@ def decode_attention(query, relative_states, proj, k_cache, v_cache, position, p
         key = (q.device, need)
         workspace = _workspaces.get(key)
         if workspace is None:
-            workspace = _workspaces[key] = torch.empty(need, dtype=torch.uint8, device=q.device)
+            workspace = _workspaces[key] = torch.zeros(need, dtype=torch.uint8, device=q.device)   # arrival counters start at zero
     _abi.require_cuda(q, r, proj, k_cache, v_cache, position, pad_counts, out)
     _abi.check(_abi.lib().ink_decode_attention(
         q.data_ptr(), r.data_ptr(), proj.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), position.data_ptr(),
