@@ -81,3 +81,22 @@ def test_decode_attention_at_the_model_shapes_against_the_oracle(ib):
         torch.cuda.synchronize()
         got = got[:, :, 0].float().cpu()
         assert (got - want).abs().max() <= TOL * want.abs().max(), (window, float((got - want).abs().max()), float(want.abs().max()))
+
+
+def test_decode_attention_rejects_what_it_was_not_built_for(ib):
+    device = torch.device("cuda", 0)
+    pos = torch.tensor(3, dtype=torch.int64, device=device)
+
+    def call(c=64, slots=128, window=0, heads=4, hk=2):
+        z = lambda *shape: torch.zeros(*shape, dtype=torch.bfloat16, device=device)
+        return ib.kernels.decode_attention(z(1, heads, c), z(1, heads, 16), z(16, 32), z(1, hk, slots, c), z(1, hk, slots, c), pos,
+                                           None, window=window)
+
+    call()                                                     # the supported form goes through
+    with pytest.raises(RuntimeError, match="head_dim"):
+        call(c=96)
+    with pytest.raises(RuntimeError, match="window"):
+        call(window=256)                                       # a ring longer than the cache
+    with pytest.raises(RuntimeError, match="kv_heads"):
+        call(heads=5, hk=2)
+    torch.cuda.synchronize()
