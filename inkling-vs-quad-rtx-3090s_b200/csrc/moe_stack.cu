@@ -539,6 +539,9 @@ __device__ __forceinline__ bool poll_router_words(const StackArgs& a, const unsi
 // The top_k largest scores over the lanes' registers (ties: the lower expert id); lane r returns choice r.
 template <int K>
 __device__ __forceinline__ int select_top_k(float (&sc)[K], int top_k) {
+  // Every round: the lane's own best, then the warp's with two hardware reductions (largest score as an
+  // order-preserving integer, then the lowest expert id among the lanes that hold it) instead of five rounds of
+  // paired shuffles: this chain sits on the critical path of every layer once the experts are sliced thin.
   const int lane = threadIdx.x & 31;
   int my_choice = 0;
 #pragma unroll 1
@@ -552,20 +555,15 @@ __device__ __forceinline__ int select_top_k(float (&sc)[K], int top_k) {
         best_e = i * 32 + lane;
       }
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-      if (ov > best || (ov == best && oe < best_e)) {
-        best = ov;
-        best_e = oe;
-      }
-    }
-    if (best_e == 0x7fffffff) best_e = r;
+    const unsigned bits = __float_as_uint(best);
+    const unsigned key = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);   // a > b  <=>  key(a) > key(b)
+    const unsigned top = __reduce_max_sync(0xffffffffu, key);
+    int winner = (int)__reduce_min_sync(0xffffffffu, key == top ? (unsigned)best_e : 0x7fffffffu);
+    if (winner == 0x7fffffff) winner = r;
 #pragma unroll
     for (int i = 0; i < K; ++i)
-      if (i * 32 + lane == best_e) sc[i] = -INFINITY;
-    if (lane == r) my_choice = best_e;
+      if (i * 32 + lane == winner) sc[i] = -INFINITY;
+    if (lane == r) my_choice = winner;
   }
   return my_choice;
 }
