@@ -194,8 +194,9 @@ int ink_short_conv(const void* x, int x_is_fp32, const float* taps, float* histo
  *   full layers with n_floor > 0: tau = 1 + alpha * log(max((position + 1) / n_floor, 1)); q and bias times tau
  *   out = softmax(scale * q . K^T + bias, over the allowed slots) . V            (FP32 inside, BF16 out)
  *  q BF16 [batch, heads, head_dim] (after q_norm), r BF16 [batch, heads, d_rel], proj BF16 [d_rel, rel_extent],
- *  k_cache / v_cache BF16 [batch, kv_heads, slots, head_dim] with the current token already stored
- *  (ink_update_kv), position: device int64 scalar = tokens stored before this one (a CUDA graph advances it),
+ *  k_cache / v_cache BF16 [batch, kv_heads, slots, head_dim]: either the current token is already stored
+ *  (ink_update_kv; new_k = new_v = NULL), or its key and value are given as new_k / new_v BF16 [batch, kv_heads,
+ *  head_dim] and this call stores them at slot `position` (modulo the window) as well, saving the launch, position: device int64 scalar = tokens stored before this one (a CUDA graph advances it),
  *  pad_counts int64 [batch] or NULL, out BF16 [batch, heads, head_dim]. head_dim 64, 128 or 256.
  *  The cache is cut into groups of 64 slots, one block per (head, sequence, group); with more than
  *  one group the partial results pass through `workspace` (ink_decode_attention_workspace_bytes, 16-byte aligned) and
@@ -203,10 +204,11 @@ int ink_short_conv(const void* x, int x_is_fp32, const float* taps, float* histo
  *  use (it starts with one arrival counter per (sequence, head)); every launch leaves the counters zero again, so the
  *  same workspace serves call after call on one stream. */
 size_t ink_decode_attention_workspace_bytes(int batch, int heads, int head_dim, int slots);
-int ink_decode_attention(const void* q, const void* r, const void* proj, const void* k_cache, const void* v_cache,
+int ink_decode_attention(const void* q, const void* r, const void* proj, void* k_cache, void* v_cache,
                          const int64_t* position, const int64_t* pad_counts, void* out, int batch, int heads,
                          int kv_heads, int head_dim, int d_rel, int rel_extent, int slots, int window, int n_floor,
-                         float alpha, float scale, void* workspace, size_t workspace_bytes, ink_stream_t stream);
+                         float alpha, float scale, const void* new_k, const void* new_v, void* workspace,
+                         size_t workspace_bytes, ink_stream_t stream);
 /* The decode step of update_kv (kernels/decode.py:149-230): the new token's key and value, BF16
  * [batch, kv_heads, head_dim], into slot `position` (modulo the window in a sliding layer) of both caches. */
 int ink_update_kv(const void* new_k, const void* new_v, void* k_cache, void* v_cache, const int64_t* position,

@@ -21,6 +21,10 @@ struct AttnArgs {
   const uint16_t* v;
   const int64_t* position;  // device scalar: tokens stored before this one
   const int64_t* pad_counts;   // [bs] or null
+  const uint16_t* new_k;    // [bs, hk, c] the current token's key and value, or null when the caches hold them already
+  const uint16_t* new_v;
+  uint16_t* k_store;        // the caches again, writable: where the current token is stored when new_k is given
+  uint16_t* v_store;
   float* partial;           // [bs, h, splits, 2 + c]: maximum, sum of exponentials, unnormalised weighted values
   unsigned* arrived;        // [bs, h] blocks of a (sequence, head) that have stored their partial; zero between launches
   uint16_t* out;            // [bs, h, c]
@@ -63,13 +67,24 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(AttnArgs
   // ---- everything from memory, in flight together
   const uint16_t* keys = a.k + ((size_t)b * a.kv_heads + kv_head) * a.slots * C;
   const uint16_t* values = a.v + ((size_t)b * a.kv_heads + kv_head) * a.slots * C;
+  // The current token may not be in the caches yet (new_k / new_v given): every block takes its row from there, and
+  // the block of the group's first head whose slots include it stores it for the steps to come.
+  const int fresh_slot = a.new_k ? (a.window ? ring_position : position) : -1;
+  const uint16_t* fresh_k = a.new_k ? a.new_k + ((size_t)b * a.kv_heads + kv_head) * C : nullptr;
+  const uint16_t* fresh_v = a.new_k ? a.new_v + ((size_t)b * a.kv_heads + kv_head) * C : nullptr;
+  if (a.new_k && head % (a.heads / a.kv_heads) == 0 && fresh_slot >= slot_base && fresh_slot < slot_base + kAttnSlots &&
+      fresh_slot < a.slots && tid < kWords) {
+    const size_t at = (((size_t)b * a.kv_heads + kv_head) * a.slots + fresh_slot) * C;
+    reinterpret_cast<uint32_t*>(a.k_store + at)[tid] = __ldg(reinterpret_cast<const uint32_t*>(fresh_k) + tid);
+    reinterpret_cast<uint32_t*>(a.v_store + at)[tid] = __ldg(reinterpret_cast<const uint32_t*>(fresh_v) + tid);
+  }
   bool k_allowed[kAttnKeys];
   uint32_t kw[kAttnKeys][kPerLane];
 #pragma unroll
   for (int j = 0; j < kAttnKeys; ++j) {
     const int slot = slot_base + warp * kAttnKeys + j;
     k_allowed[j] = allowed_at(slot);
-    const uint32_t* row = reinterpret_cast<const uint32_t*>(keys + (size_t)slot * C);
+    const uint32_t* row = reinterpret_cast<const uint32_t*>(slot == fresh_slot ? fresh_k : keys + (size_t)slot * C);
 #pragma unroll
     for (int i = 0; i < kPerLane; ++i) kw[j][i] = (k_allowed[j] && i * 32 + lane < kWords) ? __ldg(row + i * 32 + lane) : 0u;
   }
@@ -79,7 +94,7 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(AttnArgs
   for (int n = 0; n < kValues; ++n) {
     const int slot = slot_base + part + n * kParts;
     // (a slot that is not allowed may hold anything: it is not read)
-    vw[n] = allowed_at(slot) ? __ldg(reinterpret_cast<const uint32_t*>(values + (size_t)slot * C) + pair) : 0u;
+    vw[n] = allowed_at(slot) ? __ldg(reinterpret_cast<const uint32_t*>(slot == fresh_slot ? fresh_v : values + (size_t)slot * C) + pair) : 0u;
   }
   // logarithmic scaling of full-attention layers: query and bias times tau, each rounded to BF16 (the reference
   // multiplies in FP32 and casts back, my_inkling/model.py:583-590)
@@ -255,11 +270,11 @@ extern "C" size_t ink_decode_attention_workspace_bytes(int batch, int heads, int
   return splits <= 1 ? 0 : attention_counter_bytes(batch, heads) + sizeof(float) * (size_t)batch * heads * splits * (kAttnPartial + head_dim);
 }
 
-extern "C" int ink_decode_attention(const void* q, const void* r, const void* proj, const void* k_cache,
-                                    const void* v_cache, const int64_t* position, const int64_t* pad_counts, void* out,
+extern "C" int ink_decode_attention(const void* q, const void* r, const void* proj, void* k_cache,
+                                    void* v_cache, const int64_t* position, const int64_t* pad_counts, void* out,
                                     int batch, int heads, int kv_heads, int head_dim, int d_rel, int rel_extent, int slots,
-                                    int window, int n_floor, float alpha, float scale, void* workspace,
-                                    size_t workspace_bytes, ink_stream_t stream) {
+                                    int window, int n_floor, float alpha, float scale, const void* new_k,
+                                    const void* new_v, void* workspace, size_t workspace_bytes, ink_stream_t stream) {
   INK_REQUIRE(q && r && proj && k_cache && v_cache && position && out, kBadArgument, "decode_attention: null pointer argument");
   INK_REQUIRE(batch >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0, kBadArgument,
               "decode_attention: batch=%d heads=%d kv_heads=%d", batch, heads, kv_heads);
@@ -267,6 +282,7 @@ extern "C" int ink_decode_attention(const void* q, const void* r, const void* pr
               "decode_attention: head_dim=%d unsupported (built for 64, 128 and 256)", head_dim);
   INK_REQUIRE(d_rel > 0 && rel_extent > 0 && slots > 0 && window >= 0 && (window == 0 || window <= slots), kBadArgument,
               "decode_attention: d_rel=%d rel_extent=%d slots=%d window=%d", d_rel, rel_extent, slots, window);
+  INK_REQUIRE((new_k == nullptr) == (new_v == nullptr), kBadArgument, "decode_attention: new_k and new_v come together");
   const int splits = (slots + kAttnSlots - 1) / kAttnSlots;
   INK_REQUIRE(splits <= 65535 && batch <= 65535, kUnsupportedShape, "decode_attention: %d slots or %d sequences exceed the grid", slots, batch);
   const size_t need = ink_decode_attention_workspace_bytes(batch, heads, head_dim, slots);
@@ -276,7 +292,8 @@ extern "C" int ink_decode_attention(const void* q, const void* r, const void* pr
               kMisaligned, "decode_attention: buffers must be 16-byte aligned");
   if (batch == 0) return kOk;
   AttnArgs a{(const uint16_t*)q, (const uint16_t*)r, (const uint16_t*)proj, (const uint16_t*)k_cache, (const uint16_t*)v_cache,
-             position, pad_counts, (float*)((char*)workspace + attention_counter_bytes(batch, heads)), (unsigned*)workspace, (uint16_t*)out, heads, kv_heads, head_dim, d_rel, rel_extent, slots, window,
+             position, pad_counts, (const uint16_t*)new_k, (const uint16_t*)new_v, (uint16_t*)k_cache, (uint16_t*)v_cache,
+             (float*)((char*)workspace + attention_counter_bytes(batch, heads)), (unsigned*)workspace, (uint16_t*)out, heads, kv_heads, head_dim, d_rel, rel_extent, slots, window,
              n_floor, splits, alpha, scale};
   const dim3 grid(heads, batch, splits);
   if (head_dim == 64) decode_attention_kernel<64><<<grid, kAttnThreads, 0, (cudaStream_t)stream>>>(a);

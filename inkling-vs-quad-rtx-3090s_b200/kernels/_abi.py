@@ -32,7 +32,7 @@ _SIGNATURES = {
     "ink_add_rmsnorm": (I, [P, P, P, F, P, I, I, P]),
     "ink_short_conv": (I, [P, I, P, P, P, P, I, I, I, P]),
     "ink_decode_attention_workspace_bytes": (Z, [I, I, I, I]),
-    "ink_decode_attention": (I, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, P, Z, P]),
+    "ink_decode_attention": (I, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, P, P, P, Z, P]),
     "ink_update_kv": (I, [P, P, P, P, P, I, I, I, I, I, P]),
     "ink_expert_gemm_scratch_bytes": (Z, [I]),
     "ink_expert_gemm": (I, [P, I, P, P, P, P, P, I, I, I, I, I, I, I, P, Z, P, P]),

@@ -30,12 +30,15 @@ def update_kv(key, value, k_cache, v_cache, start, window: int = 0) -> None:
 
 
 def decode_attention(query, relative_states, proj, k_cache, v_cache, position, pad_counts=None, *, window: int = 0,
-                     log_scaling_n_floor=None, log_scaling_alpha: float = 0.1, scale: float | None = None, out=None):
+                     log_scaling_n_floor=None, log_scaling_alpha: float = 0.1, scale: float | None = None, out=None,
+                     new_key=None, new_value=None):
     """query BF16 [bs, h, 1, c] or [bs, h, c] (after q_norm), relative_states BF16 [bs, 1, h, d_rel] or [bs, h, d_rel],
     proj BF16 [d_rel, rel_extent] (`rel_logits_proj.proj`), caches BF16 [bs, hk, slots, c] holding the current token,
     position the device int64 counter, pad_counts int64 [bs] or None -> BF16 [bs, h, 1, c] (what the reference's
     `scaled_dot_product_attention` call returns). `window` > 0: sliding layer (ring); else full attention, scaled
-    logarithmically when `log_scaling_n_floor` is set. `scale` defaults to 1 / head_dim (my_inkling/model.py:448)."""
+    logarithmically when `log_scaling_n_floor` is set. `scale` defaults to 1 / head_dim (my_inkling/model.py:448).
+    With `new_key` / `new_value` BF16 [bs, hk, 1, c] the caches need not hold the current token yet: the call uses them
+    for its slot and stores them there (the reference's `update_kv` + attention in one launch)."""
     bs, h = query.shape[0], query.shape[1]
     c = query.shape[-1]
     q = query.reshape(bs, h, c).contiguous()
@@ -49,6 +52,11 @@ def decode_attention(query, relative_states, proj, k_cache, v_cache, position, p
     assert isinstance(position, torch.Tensor) and position.dtype == torch.int64
     if pad_counts is not None:
         assert pad_counts.dtype == torch.int64 and pad_counts.numel() == bs and pad_counts.is_contiguous()
+    new_k = new_v = None
+    if new_key is not None:
+        new_k = new_key.reshape(bs, hk, c).contiguous()
+        new_v = new_value.reshape(bs, hk, c).contiguous()
+        assert new_k.dtype == new_v.dtype == torch.bfloat16
     if out is None:
         out = torch.empty((bs, h, 1, c), dtype=torch.bfloat16, device=q.device)
     need = _abi.lib().ink_decode_attention_workspace_bytes(bs, h, c, slots)
@@ -58,10 +66,10 @@ def decode_attention(query, relative_states, proj, k_cache, v_cache, position, p
         workspace = _workspaces.get(key)
         if workspace is None:
             workspace = _workspaces[key] = torch.zeros(need, dtype=torch.uint8, device=q.device)   # arrival counters start at zero
-    _abi.require_cuda(q, r, proj, k_cache, v_cache, position, pad_counts, out)
+    _abi.require_cuda(q, r, proj, k_cache, v_cache, position, pad_counts, out, new_k, new_v)
     _abi.check(_abi.lib().ink_decode_attention(
         q.data_ptr(), r.data_ptr(), proj.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), position.data_ptr(),
         _abi.ptr(pad_counts), out.data_ptr(), bs, h, hk, c, d_rel, extent, slots, int(window),
         int(log_scaling_n_floor or 0), float(log_scaling_alpha), float(scale if scale is not None else 1.0 / c),
-        _abi.ptr(workspace), need, _abi.stream()))
+        _abi.ptr(new_k), _abi.ptr(new_v), _abi.ptr(workspace), need, _abi.stream()))
     return out

@@ -61,6 +61,28 @@ def test_update_kv_stores_the_token_where_the_reference_does(ib, kind, step):
     assert torch.equal(k.cpu(), f["k_cache"]) and torch.equal(v.cpu(), f["v_cache"])
 
 
+@pytest.mark.parametrize("kind,step", CASES)
+def test_decode_attention_that_stores_the_token_itself(ib, kind, step):
+    """The caches as they were BEFORE the reference's update_kv (the token's slot zeroed) plus the token's key and
+    value: same result as with the stored token, and the caches end up as the reference left them."""
+    device = torch.device("cuda", 0)
+    c, f = ac.CASES[kind], load(kind, step)
+    slot = f["position"] % c["window"] if c["window"] else f["position"]
+    k, v = f["k_cache"].clone(), f["v_cache"].clone()
+    k[:, :, slot] = 0
+    v[:, :, slot] = 0
+    k, v = k.to(device), v.to(device)
+    pos = torch.tensor(f["position"], dtype=torch.int64, device=device)
+    pad = torch.tensor(c["pad_counts"], dtype=torch.int64, device=device)
+    got = ib.kernels.decode_attention(f["q"].to(device), f["r"].to(device), f["proj"].to(device), k, v, pos, pad, window=c["window"],
+                                      log_scaling_n_floor=c["n_floor"], log_scaling_alpha=c["alpha"], scale=ac.SCALE,
+                                      new_key=f["new_k"].to(device).unsqueeze(2), new_value=f["new_v"].to(device).unsqueeze(2))
+    torch.cuda.synchronize()
+    want = f["out"].float()
+    assert (got[:, :, 0].float().cpu() - want).abs().max() <= TOL * want.abs().max()
+    assert torch.equal(k.cpu(), f["k_cache"]) and torch.equal(v.cpu(), f["v_cache"])
+
+
 def test_decode_attention_at_the_model_shapes_against_the_oracle(ib):
     """64 heads of 128 channels over 16 key/value heads, a full ring of 512 slots, 16 relative patterns: seeded
     inputs, compared with the float64 oracle; and a full-attention layer of 4 096 slots with the scaling on."""
