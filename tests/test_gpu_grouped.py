@@ -119,6 +119,33 @@ def test_batched_decode_64_tokens_zipf_at_full_shapes(ib, device):
         del cpu_banks
 
 
+def test_a_prompt_of_2048_tokens_at_full_shapes(ib, device):
+    """12 288 routes through one block of the full shapes (a prefill-sized batch: the planner's large path, the
+    grouped block-scaled kernel with up to hundreds of routes per expert): sampled tokens against the float64
+    oracle, and the whole batch against itself in two halves (the result of a token does not depend on its batch)."""
+    d, f, E, k, tokens = 4096, 2048, 256, 6, 2048
+    banks = ib.make_expert_banks(E, d, f, device, seed=2)
+    experts = ib.ResidentExperts(d, f, None, banks.weights)
+    gen = torch.Generator().manual_seed(2048)
+    x = torch.randn(tokens, d, generator=gen).to(BF16).to(device)
+    idx = _skewed_routing(gen, tokens, E, k).to(device)
+    w = torch.rand(tokens, k, generator=gen).to(BF16).to(device)
+    whole = experts(x, idx, w).float().clone()
+    torch.cuda.synchronize()
+    experts.check_status()
+    assert torch.isfinite(whole).all()
+    halves = torch.cat([experts(x[a:a + 1024], idx[a:a + 1024].contiguous(), w[a:a + 1024].contiguous()).float().clone()
+                        for a in (0, 1024)])
+    torch.cuda.synchronize()
+    assert max_rel(whole, halves) <= 1e-2
+    for token in (0, 1023, 2047):
+        ids = idx[token].cpu()
+        cpu_banks = {int(e): {n: t.cpu() for n, t in banks.weights[int(e)].items()} for e in ids.tolist()}
+        want = oracle_moe.routed_experts_fp32(x[token:token + 1].cpu(), ids.view(1, -1), w[token:token + 1].cpu(), cpu_banks)
+        assert max_rel(whole[token:token + 1], want) <= TOL
+        del cpu_banks
+
+
 @pytest.mark.parametrize("d,f,E,tokens", [(1024, 512, 32, 40), (2048, 256, 16, 24), (1024, 512, 32, 200)])
 def test_block_scaled_projections_against_oracle(ib, device, d, f, E, tokens):
     """ink_expert_gemm_tc: the packed banks straight into tcgen05.mma.kind::mxf4nvf4.block_scale (banks of one
