@@ -368,6 +368,11 @@ __device__ __forceinline__ void st_tagged(unsigned long long* p, float v, unsign
 __device__ __forceinline__ void st_tagged_sys(unsigned long long* p, float v, unsigned tag) {   // into a peer's memory
   asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p), "l"(tagged(v, tag)) : "memory");
 }
+// two neighbouring words in one 16-byte store (p 16-byte aligned): each word carries its own tag, so it does not
+// matter whether the two halves become visible together
+__device__ __forceinline__ void st_tagged2_sys(unsigned long long* p, float v0, float v1, unsigned tag) {
+  asm volatile("st.relaxed.sys.global.v2.b64 [%0], {%1, %2};" ::"l"(p), "l"(tagged(v0, tag)), "l"(tagged(v1, tag)) : "memory");
+}
 __device__ __forceinline__ unsigned long long ld_tagged(const unsigned long long* p) {
   unsigned long long v;
   asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
@@ -1780,10 +1785,24 @@ __global__ void __launch_bounds__(TC ? kSThreadsTc : kSThreads, 1) moe_stack_ker
         if (last_of_block && !sh.failed) {
           __syncwarp();
           // hand this block's rows over (to every rank, itself included), then sum what the ranks sent for them
-          for (int row = lane; row < plan.n_g * S::RT; row += 32) {
-            float total = 0.f;
-            for (int j = 0; j < n_jobs; ++j) total += sh.contrib[j][row];
-            send_row<D>(a, xpar, tag, plan.g0 * S::RT + row, total);
+          if (a.world == 1) {
+            for (int row = lane; row < plan.n_g * S::RT; row += 32) {
+              float total = 0.f;
+              for (int j = 0; j < n_jobs; ++j) total += sh.contrib[j][row];
+              send_row<D>(a, xpar, tag, plan.g0 * S::RT + row, total);
+            }
+          } else {
+            // to the peers two rows at a time (the block's rows start at a multiple of RT, RT is even): half as
+            // many packets on the links
+            for (int pair = lane; pair < plan.n_g * S::RT / 2; pair += 32) {
+              float t0 = 0.f, t1 = 0.f;
+              for (int j = 0; j < n_jobs; ++j) {
+                t0 += sh.contrib[j][2 * pair];
+                t1 += sh.contrib[j][2 * pair + 1];
+              }
+              const size_t at = ((size_t)xpar * a.world + a.rank) * D + (size_t)plan.g0 * S::RT + 2 * pair;
+              for (int r = 0; r < a.world; ++r) st_tagged2_sys(a.peer_inbox[r] + at, t0, t1, tag);
+            }
           }
           if (lane == 0) INK_TRACE(layer, kTrRowsSent);
           if (a.world > 1)
