@@ -1,0 +1,77 @@
+"""The decode step of the reference's attention module on this library's kernels.
+
+`MyInklingAttention.forward` with a decoding cache (my_inkling/model.py:504-622) is: the fused QKVR projection,
+RMS norm of the query heads, short convolution + RMS norm of the key, short convolution of the value, `update_kv`,
+relative-position bias + mask + `scaled_dot_product_attention`, the output projection (and its all-reduce under
+tensor parallelism). Here the two dense projections stay library GEMVs (`torch.nn.functional.linear`), everything
+between them runs in this library: `ink_short_conv`, `ink_add_rmsnorm`, `ink_decode_attention` (which also stores
+the token in the caches). The cache object is the reference's `MyInklingCache` (or anything with the same fields:
+`layers[i].k_cache / v_cache / conv_caches[0 | 1].cache`, `position`, `pad_counts`).
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .kernels import add_rmsnorm, decode_attention, short_conv
+from .kernels.paired_all_reduce import all_reduce
+
+
+class DecodeAttention(nn.Module):
+    def __init__(self, qkvr_weight, o_weight, q_norm_weight, k_norm_weight, k_taps, v_taps, rel_proj, *, layer_idx: int,
+                 heads: int, kv_heads: int, head_dim: int, d_rel: int, window: int = 0, log_scaling_n_floor=None,
+                 log_scaling_alpha: float = 0.1, eps: float = 1e-6, group=None):
+        """Weights as the reference module holds them after `fuse_projections`: qkvr_weight BF16
+        [(h + 2 hk) c + h d_rel, d], o_weight BF16 [d, h c], norm weights BF16 [c], taps FP32 [hk c, 1, K],
+        rel_proj BF16 [d_rel, rel_extent]. `window` > 0 for a sliding layer. `group`: the tensor-parallel process
+        group whose ranks hold slices of the heads (the output projection's partial sums are all-reduced)."""
+        super().__init__()
+        self.layer_idx, self.heads, self.kv_heads, self.head_dim, self.d_rel = layer_idx, heads, kv_heads, head_dim, d_rel
+        self.window, self.n_floor, self.alpha, self.eps, self.group = window, log_scaling_n_floor, log_scaling_alpha, eps, group
+        self.sizes = [heads * head_dim, kv_heads * head_dim, kv_heads * head_dim, heads * d_rel]
+        assert qkvr_weight.shape[0] == sum(self.sizes)
+        for name, t in (("qkvr_weight", qkvr_weight), ("o_weight", o_weight), ("q_norm_weight", q_norm_weight),
+                        ("k_norm_weight", k_norm_weight), ("k_taps", k_taps), ("v_taps", v_taps), ("rel_proj", rel_proj)):
+            self.register_buffer(name, t.contiguous())
+        self._zeros = None
+
+    @classmethod
+    def from_reference(cls, attention, group=None) -> "DecodeAttention":
+        """From a `MyInklingAttention` whose projections are fused (`fuse_projections`), on its device."""
+        return cls(attention.qkvr_proj.weight.detach(), attention.o_proj.weight.detach(), attention.q_norm.weight.detach(),
+                   attention.k_norm.weight.detach(), attention.k_sconv.conv1d.weight.detach(),
+                   attention.v_sconv.conv1d.weight.detach(), attention.rel_logits_proj.proj.detach(),
+                   layer_idx=attention.layer_idx, heads=attention.num_heads, kv_heads=attention.num_key_value_heads,
+                   head_dim=attention.head_dim, d_rel=attention.rel_logits_proj.d_rel, window=attention.sliding_window or 0,
+                   log_scaling_n_floor=attention.log_scaling_n_floor, log_scaling_alpha=attention.log_scaling_alpha,
+                   eps=attention.q_norm.variance_epsilon, group=group)
+
+    def _norm(self, rows: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+        """RMS norm over the last dimension of BF16 [n, c] with the reference's rounding (kernels/decode.py:36-43)."""
+        if self._zeros is None or self._zeros.shape[0] < rows.shape[0]:
+            self._zeros = torch.zeros(rows.shape[0], rows.shape[1], dtype=torch.float32, device=rows.device)
+        normed = torch.empty_like(rows)
+        add_rmsnorm(self._zeros[: rows.shape[0]], rows, weight, self.eps, normed)   # rows + 0, then the norm
+        return normed
+
+    def forward(self, hidden_states: torch.Tensor, cache) -> torch.Tensor:
+        """hidden_states BF16 [bs, 1, d], cache in decode mode -> BF16 [bs, 1, d]; the caches and the convolution
+        histories of this layer are updated in place, `cache.position` is left to the caller (`cache.advance`)."""
+        bs, s, _ = hidden_states.shape
+        assert s == 1, "one token per sequence"
+        layer = cache.layers[self.layer_idx]
+        h, hk, c = self.heads, self.kv_heads, self.head_dim
+        q, k, v, r = F.linear(hidden_states, self.qkvr_weight).split(self.sizes, dim=-1)
+        q = self._norm(q.reshape(bs * h, c).contiguous(), self.q_norm_weight)
+        k = short_conv(k.contiguous(), self.k_taps, layer.conv_caches[0].cache, None)
+        k = self._norm(k.reshape(bs * hk, c), self.k_norm_weight)
+        v = short_conv(v.contiguous(), self.v_taps, layer.conv_caches[1].cache, None)
+        out = decode_attention(q.view(bs, h, c), r.reshape(bs, h, self.d_rel), self.rel_proj, layer.k_cache, layer.v_cache,
+                               cache.position, cache.pad_counts, window=self.window, log_scaling_n_floor=self.n_floor,
+                               log_scaling_alpha=self.alpha, scale=1.0 / c, new_key=k.view(bs, hk, 1, c),
+                               new_value=v.reshape(bs, hk, 1, c))
+        y = F.linear(out.reshape(bs, 1, h * c), self.o_weight)
+        if self.group is not None:
+            y = all_reduce(y, self.group)   # (nothing to do with one rank)
+        return y

@@ -6,7 +6,7 @@
 with a short prompt, frozen for decode and stepped token by token, once for a sliding-window layer (the ring
 wraps during the run) and once for a full-attention layer with the logarithmic scaling on. Its Triton kernels
 (`update_kv`, `short_conv`) run under TRITON_INTERPRET=1. At chosen steps the inputs of the attention core are
-recorded with hooks -- the normed queries, the relative states, the caches as `scaled_dot_product_attention`
+recorded with hooks -- the module's input and output, the convolution histories, the normed queries, the relative states, the caches as `scaled_dot_product_attention`
 sees them, the position counter -- together with what `scaled_dot_product_attention` returned and what
 `update_kv` was given. Writes tests/golden/attention.npz (BF16 tensors as their uint16 bit patterns).
 """
@@ -37,7 +37,7 @@ out: dict[str, np.ndarray] = {}
 
 
 def put(key: str, t: torch.Tensor) -> None:
-    t = t.detach().cpu().contiguous()
+    t = t.detach().cpu().contiguous().clone()
     out[key] = t.view(torch.uint16).numpy() if t.dtype == torch.bfloat16 else t.numpy()
 
 
@@ -59,6 +59,13 @@ def run(kind: str) -> None:
     attn.v_sconv.conv1d.float()
     attn.fuse_projections()
     put(f"{kind}/proj", attn.rel_logits_proj.proj)
+    # the whole module's weights, for the test that runs the decode step end to end
+    put(f"{kind}/qkvr_weight", attn.qkvr_proj.weight)
+    put(f"{kind}/o_weight", attn.o_proj.weight)
+    put(f"{kind}/q_norm_weight", attn.q_norm.weight)
+    put(f"{kind}/k_norm_weight", attn.k_norm.weight)
+    put(f"{kind}/k_taps", attn.k_sconv.conv1d.weight)      # FP32 [hk * c, 1, K]
+    put(f"{kind}/v_taps", attn.v_sconv.conv1d.weight)
     cache = MyInklingCache(config, batch_size=c["batch"], capacity=c["capacity"], pad_counts=torch.tensor(c["pad_counts"]),
                            dtype=torch.bfloat16, device="cpu")
     rec: dict[str, torch.Tensor] = {}
@@ -83,8 +90,14 @@ def run(kind: str) -> None:
         cache.prepare_decode()
         for step in range(max(c["record"]) + 1):
             position = int(cache.position)
-            attn(torch.randn(c["batch"], 1, c["hidden"], generator=gen).bfloat16(), cache=cache)
+            hidden = torch.randn(c["batch"], 1, c["hidden"], generator=gen).bfloat16()
+            if step in c["record"]:     # the convolutions' histories as the step finds them
+                put(f"{kind}/{step}/k_history", cache.layers[layer_idx].conv_caches[0].cache)
+                put(f"{kind}/{step}/v_history", cache.layers[layer_idx].conv_caches[1].cache)
+            y = attn(hidden, cache=cache)
             if step in c["record"]:
+                put(f"{kind}/{step}/hidden", hidden[:, 0])
+                put(f"{kind}/{step}/y", y[:, 0])
                 r = rec["qkvr"].split(attn.projection_sizes, dim=-1)[3].view(c["batch"], c["heads"], c["d_rel"])
                 put(f"{kind}/{step}/position", torch.tensor(position))
                 put(f"{kind}/{step}/q", rec["q"][:, :, 0])                 # [bs, h, c] after q_norm

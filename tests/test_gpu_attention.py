@@ -122,3 +122,50 @@ def test_decode_attention_rejects_what_it_was_not_built_for(ib):
     with pytest.raises(RuntimeError, match="kv_heads"):
         call(heads=5, hk=2)
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("kind,step", CASES)
+def test_the_whole_decode_step_of_the_attention_module(ib, kind, step):
+    """Hidden state in, hidden state out, like `MyInklingAttention.forward` with a decoding cache: the module's weights,
+    the caches and convolution histories as the reference's step found them, its input and its output are in the
+    fixture. (The reference ran its short convolution under the Triton interpreter, which truncates where the GPU
+    rounds: the key and value of the current token may differ from the recorded ones in the last BF16 bit.)"""
+    from types import SimpleNamespace
+
+    import numpy as np
+    from test_attention_oracle import GOLDEN_DIR
+
+    device = torch.device("cuda", 0)
+    c, f = ac.CASES[kind], load(kind, step)
+    z = np.load(GOLDEN_DIR / "attention.npz")
+
+    def t(name, bf16=True):
+        a = torch.from_numpy(z[name].copy())
+        return (a.view(torch.bfloat16) if bf16 else a).to(device)
+
+    module = ib.DecodeAttention(
+        t(f"{kind}/qkvr_weight"), t(f"{kind}/o_weight"), t(f"{kind}/q_norm_weight"), t(f"{kind}/k_norm_weight"),
+        t(f"{kind}/k_taps", False), t(f"{kind}/v_taps", False), f["proj"].to(device), layer_idx=0, heads=c["heads"],
+        kv_heads=c["kv_heads"], head_dim=c["head_dim"], d_rel=c["d_rel"], window=c["window"],
+        log_scaling_n_floor=c["n_floor"], log_scaling_alpha=c["alpha"])
+    slot = f["position"] % c["window"] if c["window"] else f["position"]
+    k, v = f["k_cache"].clone(), f["v_cache"].clone()
+    k[:, :, slot] = 0
+    v[:, :, slot] = 0
+    layer = SimpleNamespace(k_cache=k.to(device), v_cache=v.to(device),
+                            conv_caches=[SimpleNamespace(cache=t(f"{kind}/{step}/k_history", False)),
+                                         SimpleNamespace(cache=t(f"{kind}/{step}/v_history", False))])
+    cache = SimpleNamespace(layers=[layer], position=torch.tensor(f["position"], dtype=torch.int64, device=device),
+                            pad_counts=torch.tensor(c["pad_counts"], dtype=torch.int64, device=device))
+    y = module(t(f"{kind}/{step}/hidden").unsqueeze(1), cache)
+    torch.cuda.synchronize()
+    want = t(f"{kind}/{step}/y").float().cpu()
+    got = y[:, 0].float().cpu()
+    assert (got - want).abs().max() <= TOL * want.abs().max()
+    # the token landed in its slot, up to the last bit; every other slot is untouched
+    stored_k, stored_v = layer.k_cache.cpu(), layer.v_cache.cpu()
+    assert (stored_k[:, :, slot].float() - f["new_k"].float()).abs().max() <= 2 ** -6 * f["new_k"].float().abs().max()
+    assert (stored_v[:, :, slot].float() - f["new_v"].float()).abs().max() <= 2 ** -6 * f["new_v"].float().abs().max()
+    stored_k[:, :, slot] = f["k_cache"][:, :, slot]
+    stored_v[:, :, slot] = f["v_cache"][:, :, slot]
+    assert torch.equal(stored_k, f["k_cache"]) and torch.equal(stored_v, f["v_cache"])
