@@ -75,3 +75,35 @@ class DecodeAttention(nn.Module):
         if self.group is not None:
             y = all_reduce(y, self.group)   # (nothing to do with one rank)
         return y
+
+
+class DecodeLayer(nn.Module):
+    """One sparse decoder layer at decode, `MyInklingDecoderLayer.forward` (my_inkling/model.py:661-675):
+    h' = attn_sconv(attention(input_norm(h)), residual=h);  out = mlp_sconv(moe(post_norm(h')), residual=h').
+    `attention` is a DecodeAttention, `moe` a FusedMoE; the two short convolutions use the layer's convolution caches
+    2 and 3 of the reference's cache object."""
+
+    def __init__(self, attention: DecodeAttention, moe, input_norm_weight, post_norm_weight, attn_taps, mlp_taps, eps: float = 1e-6):
+        super().__init__()
+        self.attention, self.moe, self.eps = attention, moe, eps
+        for name, t in (("input_norm_weight", input_norm_weight), ("post_norm_weight", post_norm_weight),
+                        ("attn_taps", attn_taps), ("mlp_taps", mlp_taps)):
+            self.register_buffer(name, t.contiguous())
+        self._zeros = None
+
+    def _norm(self, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+        rows = x.reshape(-1, x.shape[-1]).clone()          # (the norm kernel adds its FP32 input to the rows in place: zero here)
+        if self._zeros is None or self._zeros.shape != rows.shape:
+            self._zeros = torch.zeros(rows.shape, dtype=torch.float32, device=rows.device)
+        normed = torch.empty_like(rows)
+        add_rmsnorm(self._zeros, rows, weight, self.eps, normed)
+        return normed.view(x.shape)
+
+    def forward(self, hidden_states: torch.Tensor, cache) -> torch.Tensor:
+        """hidden_states BF16 [bs, 1, d] -> BF16 [bs, 1, d]; the layer's caches are updated in place."""
+        bs, _, d = hidden_states.shape
+        layer = cache.layers[self.attention.layer_idx]
+        attended = self.attention(self._norm(hidden_states, self.input_norm_weight), cache)
+        h = short_conv(attended.contiguous(), self.attn_taps, layer.conv_caches[2].cache, hidden_states.contiguous())
+        block = self.moe.forward_partial(self._norm(h, self.post_norm_weight).view(bs, d))       # FP32 [bs, d], all-reduced
+        return short_conv(block.view(bs, 1, d), self.mlp_taps, layer.conv_caches[3].cache, h)

@@ -9,3 +9,30 @@ CASES = {
                  n_floor=8, alpha=0.1, batch=2, pad_counts=[0, 3], prompt=20, record=(0, 30, 60), seed=12, std=0.08),
 }
 SCALE = 1.0 / 64   # 1 / head_dim, my_inkling/model.py:448
+
+# One whole sparse decoder layer (attention + MoE block + the norms and short convolutions around them): the MoE
+# block is cases.LAYER_CASES["mid"] (hidden 1024), the attention a sliding-window layer whose ring wraps in the run.
+LAYER = dict(moe="mid", hidden=1024, heads=8, kv_heads=4, head_dim=64, window=32, capacity=96, d_rel=16, rel_extent=32,
+             n_floor=8, alpha=0.1, batch=2, pad_counts=[0, 3], prompt=20, record=(0, 13), seed=21, std=0.04, conv_k=4, eps=1e-6)
+
+
+def layer_weights(c=LAYER):
+    """The layer's weights outside the MoE block, from the seed: the same tensors in the generator (copied into the
+    reference's modules) and in the tests."""
+    import torch
+
+    gen = torch.Generator().manual_seed(c["seed"])
+    d, h, hk, hd = c["hidden"], c["heads"], c["kv_heads"], c["head_dim"]
+
+    def w(*shape, std=c["std"], dtype=torch.bfloat16):
+        return (torch.randn(*shape, generator=gen) * std).to(dtype)
+
+    def near_one(n):
+        return (1.0 + 0.1 * torch.randn(n, generator=gen)).to(torch.bfloat16)
+
+    return dict(
+        q=w(h * hd, d), k=w(hk * hd, d), v=w(hk * hd, d), r=w(h * c["d_rel"], d), o=w(d, h * hd),
+        q_norm=near_one(hd), k_norm=near_one(hd), rel_proj=w(c["d_rel"], c["rel_extent"], std=0.5),
+        k_taps=w(hk * hd, 1, c["conv_k"], std=0.3, dtype=torch.float32), v_taps=w(hk * hd, 1, c["conv_k"], std=0.3, dtype=torch.float32),
+        input_norm=near_one(d), post_norm=near_one(d),
+        attn_taps=w(d, 1, c["conv_k"], std=0.3, dtype=torch.float32), mlp_taps=w(d, 1, c["conv_k"], std=0.3, dtype=torch.float32))

@@ -111,9 +111,62 @@ def run(kind: str) -> None:
     ref_model.F.scaled_dot_product_attention = original_sdpa
 
 
+def run_layer() -> None:
+    """A whole sparse decoder layer (my_inkling/model.py:636-675) stepped in decode mode: input, output, caches and all
+    four convolution histories as each recorded step finds them. The MoE block holds the NVFP4 banks of
+    cases.LAYER_CASES[...] dequantised to BF16, as the reference's PyTorch path does."""
+    import cases
+    import make_golden   # (the loaders of the MoE fixtures; takes the reference root from the same command line)
+
+    c = ac.LAYER
+    mc = cases.LAYER_CASES[c["moe"]]
+    config = ref_model.InklingTextConfig(
+        hidden_size=c["hidden"], vocab_size=64, num_hidden_layers=1, pad_token_id=0, layer_types=["hybrid_sliding"],
+        moe_intermediate_size=mc["f"], n_routed_experts=mc["experts"], num_experts_per_tok=mc["top_k"],
+        n_shared_experts=mc["n_shared"], route_scale=8.0, rms_norm_eps=c["eps"],
+        swa_num_attention_heads=c["heads"], swa_num_key_value_heads=c["kv_heads"], swa_head_dim=c["head_dim"],
+        sliding_window_size=c["window"], d_rel=c["d_rel"], rel_extent=c["rel_extent"], conv_kernel_size=c["conv_k"],
+        log_scaling_n_floor=c["n_floor"], log_scaling_alpha=c["alpha"])
+    layer = ref_model.MyInklingDecoderLayer(config, 0).bfloat16().eval()
+    w = ac.layer_weights(c)
+    p, banks, _ = cases.make_layer(**mc)
+    with torch.no_grad():
+        a = layer.self_attn
+        a.q_proj.weight.copy_(w["q"]); a.k_proj.weight.copy_(w["k"]); a.v_proj.weight.copy_(w["v"]); a.r_proj.weight.copy_(w["r"])
+        a.o_proj.weight.copy_(w["o"]); a.q_norm.weight.copy_(w["q_norm"]); a.k_norm.weight.copy_(w["k_norm"])
+        a.rel_logits_proj.proj.copy_(w["rel_proj"])
+        for conv, taps in ((a.k_sconv, "k_taps"), (a.v_sconv, "v_taps"), (layer.attn_sconv, "attn_taps"), (layer.mlp_sconv, "mlp_taps")):
+            conv.conv1d.float()            # the reference keeps the convolution taps in FP32
+            conv.conv1d.weight.copy_(w[taps])
+        layer.input_layernorm.weight.copy_(w["input_norm"]); layer.post_attention_layernorm.weight.copy_(w["post_norm"])
+        a.fuse_projections()
+        layer.mlp = make_golden.load_reference_moe(mc, p, banks)
+        cache = MyInklingCache(config, batch_size=c["batch"], capacity=c["capacity"], pad_counts=torch.tensor(c["pad_counts"]),
+                               dtype=torch.bfloat16, device="cpu")
+        gen = torch.Generator().manual_seed(c["seed"] + 1)
+        layer(torch.randn(c["batch"], c["prompt"], c["hidden"], generator=gen).bfloat16(), cache=cache)
+        cache.advance(c["prompt"])
+        cache.prepare_decode()
+        for step in range(max(c["record"]) + 1):
+            position = int(cache.position)
+            hidden = torch.randn(c["batch"], 1, c["hidden"], generator=gen).bfloat16()
+            if step in c["record"]:
+                for i in range(4):
+                    put(f"layer/{step}/history{i}", cache.layers[0].conv_caches[i].cache)
+            y = layer(hidden, cache=cache)
+            if step in c["record"]:
+                put(f"layer/{step}/position", torch.tensor(position))
+                put(f"layer/{step}/hidden", hidden[:, 0])
+                put(f"layer/{step}/y", y[:, 0])
+                put(f"layer/{step}/k_cache", cache.layers[0].k_cache)     # after the step: the token is in its slot
+                put(f"layer/{step}/v_cache", cache.layers[0].v_cache)
+            cache.advance(1)
+
+
 def main() -> None:
     for kind in ac.CASES:
         run(kind)
+    run_layer()
     np.savez_compressed(HERE / "attention.npz", **out)
     print(f"wrote {len(out)} arrays, {sum(a.nbytes for a in out.values()) / 1e6:.2f} MB raw")
 

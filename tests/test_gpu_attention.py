@@ -169,3 +169,54 @@ def test_the_whole_decode_step_of_the_attention_module(ib, kind, step):
     stored_k[:, :, slot] = f["k_cache"][:, :, slot]
     stored_v[:, :, slot] = f["v_cache"][:, :, slot]
     assert torch.equal(stored_k, f["k_cache"]) and torch.equal(stored_v, f["v_cache"])
+
+
+@pytest.mark.parametrize("step", ac.LAYER["record"])
+def test_a_whole_sparse_decoder_layer_at_decode(ib, step):
+    """`MyInklingDecoderLayer.forward` for one token per sequence: norm, attention, short convolution + residual, norm,
+    MoE block (NVFP4 experts here, their BF16 dequantisation in the reference), short convolution + residual. Input,
+    output, caches and the four convolution histories of the step were recorded from the reference's layer."""
+    from types import SimpleNamespace
+
+    import numpy as np
+
+    import cases
+    from helpers import banks_to_device, layer_on_device
+    from test_attention_oracle import GOLDEN_DIR
+
+    device = torch.device("cuda", 0)
+    c = ac.LAYER
+    z = np.load(GOLDEN_DIR / "attention.npz")
+
+    def t(name, bf16=True):
+        a = torch.from_numpy(z[f"layer/{step}/{name}"].copy())
+        return (a.view(torch.bfloat16) if bf16 else a).to(device)
+
+    w = {k: v.to(device) for k, v in ac.layer_weights(c).items()}
+    attention = ib.DecodeAttention(torch.cat([w["q"], w["k"], w["v"], w["r"]]), w["o"], w["q_norm"], w["k_norm"], w["k_taps"],
+                                   w["v_taps"], w["rel_proj"], layer_idx=0, heads=c["heads"], kv_heads=c["kv_heads"],
+                                   head_dim=c["head_dim"], d_rel=c["d_rel"], window=c["window"],
+                                   log_scaling_n_floor=c["n_floor"], log_scaling_alpha=c["alpha"], eps=c["eps"])
+    p, banks, _ = cases.make_layer(**cases.LAYER_CASES[c["moe"]])
+    dp = layer_on_device(p, device)
+    experts = ib.ResidentExperts(p["d"], p["f"], None, banks_to_device(banks, device))
+    moe = ib.FusedMoE(dp["router_weight"], dp["router_bias"], dp["global_scale"], p["route_scale"], p["top_k"],
+                      dp["shared_gate"], dp["shared_up"], dp["shared_down"], experts, None)
+    layer = ib.DecodeLayer(attention, moe, w["input_norm"], w["post_norm"], w["attn_taps"], w["mlp_taps"], eps=c["eps"])
+    position = int(z[f"layer/{step}/position"])
+    slot = position % c["window"]
+    k, v = t("k_cache").clone(), t("v_cache").clone()
+    k[:, :, slot] = 0
+    v[:, :, slot] = 0
+    state = SimpleNamespace(k_cache=k, v_cache=v, conv_caches=[SimpleNamespace(cache=t(f"history{i}", False)) for i in range(4)])
+    cache = SimpleNamespace(layers=[state], position=torch.tensor(position, dtype=torch.int64, device=device),
+                            pad_counts=torch.tensor(c["pad_counts"], dtype=torch.int64, device=device))
+    y = layer(t("hidden").unsqueeze(1), cache)
+    torch.cuda.synchronize()
+    experts.check_status()
+    got, want = y[:, 0].float().cpu(), t("y").float().cpu()
+    assert (got - want).abs().max() <= TOL * want.abs().max(), float((got - want).abs().max() / want.abs().max())
+    # the token's key and value are in their slot (up to the last bit, see the test above)
+    for stored, recorded in ((k, t("k_cache")), (v, t("v_cache"))):
+        a, b = stored[:, :, slot].float(), recorded[:, :, slot].float()
+        assert (a - b).abs().max() <= 2 ** -6 * b.abs().max()
