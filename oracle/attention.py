@@ -77,3 +77,47 @@ def update_kv(k_cache, v_cache, new_k, new_v, position: int, window: int) -> Non
     slot = position % window if window else position
     k_cache[:, :, slot] = new_k
     v_cache[:, :, slot] = new_v
+
+
+def rms_norm_heads(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """MyInklingRMSNorm over the last dimension (my_inkling/model.py:143-150): FP32 statistics, the normalised value
+    rounded to the input type, then times the weight."""
+    xf = x.float()
+    normed = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)
+    return weight * normed
+
+
+def short_conv_step(x: torch.Tensor, taps: torch.Tensor, history: torch.Tensor, residual=None) -> torch.Tensor:
+    """One decode token through MyInklingShortConv (kernels/decode.py:65-146): x BF16 [bs, d], taps FP32 [d, 1, K],
+    history FP32 [bs, d, K] shifted in place. total = sum_j history[j + 1] * taps[j] + x * taps[K - 1] in FP32, tap
+    order; y = bf16(total + x), with a residual y = bf16(fp32(y) + residual)."""
+    k = taps.shape[-1]
+    w = taps[:, 0]                                   # [d, K]
+    xf = x.float()
+    total = torch.zeros_like(xf)
+    for j in range(k - 1):
+        total = total + history[:, :, j + 1] * w[:, j]
+    total = total + xf * w[:, k - 1]
+    history[:, :, :-1] = history[:, :, 1:].clone()
+    history[:, :, -1] = xf
+    y = (total + xf).to(BF16)
+    return y if residual is None else (y.float() + residual.float()).to(BF16)
+
+
+def attention_decode_step(hidden, weights: dict, k_cache, v_cache, k_history, v_history, position: int, pad_counts, *,
+                          heads: int, kv_heads: int, head_dim: int, d_rel: int, window: int, n_floor, alpha: float,
+                          eps: float) -> torch.Tensor:
+    """`MyInklingAttention.forward` with a decoding cache (my_inkling/model.py:504-622), hidden BF16 [bs, d] -> BF16
+    [bs, d]; caches and histories are updated in place. `weights`: qkvr [(h + 2 hk) c + h d_rel, d], o [d, h c],
+    q_norm, k_norm [c], k_taps, v_taps FP32 [hk c, 1, K], rel_proj [d_rel, extent]."""
+    bs = hidden.shape[0]
+    h, hk, c = heads, kv_heads, head_dim
+    qkvr = (hidden.float() @ weights["qkvr"].float().T).to(BF16)
+    q, k, v, r = qkvr.split([h * c, hk * c, hk * c, h * d_rel], dim=-1)
+    q = rms_norm_heads(q.reshape(bs, h, c), weights["q_norm"], eps)
+    k = rms_norm_heads(short_conv_step(k, weights["k_taps"], k_history).reshape(bs, hk, c), weights["k_norm"], eps)
+    v = short_conv_step(v, weights["v_taps"], v_history).reshape(bs, hk, c)
+    update_kv(k_cache, v_cache, k, v, position, window)
+    out = decode_attention(q, r.reshape(bs, h, d_rel), weights["rel_proj"], k_cache, v_cache, position, pad_counts, window,
+                           n_floor, alpha, 1.0 / c)
+    return (out.reshape(bs, h * c).float() @ weights["o"].float().T).to(BF16)
