@@ -220,3 +220,65 @@ def test_a_whole_sparse_decoder_layer_at_decode(ib, step):
     for stored, recorded in ((k, t("k_cache")), (v, t("v_cache"))):
         a, b = stored[:, :, slot].float(), recorded[:, :, slot].float()
         assert (a - b).abs().max() <= 2 ** -6 * b.abs().max()
+
+
+def test_the_decoder_layer_replays_in_a_cuda_graph(ib):
+    """Warm-up steps on a side stream, capture, replay (the sequence of my_inkling/decode_graph.py:22-41): nothing in
+    the layer allocates or synchronises once it is warm, the position counter is read on the device, so a replay with
+    the caches put back gives the bits of the eager step."""
+    from types import SimpleNamespace
+
+    import cases
+    from helpers import banks_to_device, layer_on_device
+
+    device = torch.device("cuda", 0)
+    c = ac.LAYER
+    w = {k: v.to(device) for k, v in ac.layer_weights(c).items()}
+    attention = ib.DecodeAttention(torch.cat([w["q"], w["k"], w["v"], w["r"]]), w["o"], w["q_norm"], w["k_norm"], w["k_taps"],
+                                   w["v_taps"], w["rel_proj"], layer_idx=0, heads=c["heads"], kv_heads=c["kv_heads"],
+                                   head_dim=c["head_dim"], d_rel=c["d_rel"], window=c["window"],
+                                   log_scaling_n_floor=c["n_floor"], log_scaling_alpha=c["alpha"], eps=c["eps"])
+    p, banks, _ = cases.make_layer(**cases.LAYER_CASES[c["moe"]])
+    dp = layer_on_device(p, device)
+    experts = ib.ResidentExperts(p["d"], p["f"], None, banks_to_device(banks, device))
+    moe = ib.FusedMoE(dp["router_weight"], dp["router_bias"], dp["global_scale"], p["route_scale"], p["top_k"],
+                      dp["shared_gate"], dp["shared_up"], dp["shared_down"], experts, None)
+    layer = ib.DecodeLayer(attention, moe, w["input_norm"], w["post_norm"], w["attn_taps"], w["mlp_taps"], eps=c["eps"])
+    gen = torch.Generator().manual_seed(9)
+    bs, d, hk, hd = c["batch"], c["hidden"], c["kv_heads"], c["head_dim"]
+    state = SimpleNamespace(
+        k_cache=torch.randn(bs, hk, c["window"], hd, generator=gen).bfloat16().to(device),
+        v_cache=torch.randn(bs, hk, c["window"], hd, generator=gen).bfloat16().to(device),
+        conv_caches=[SimpleNamespace(cache=torch.randn(bs, n, c["conv_k"], generator=gen).to(device)) for n in (hk * hd, hk * hd, d, d)])
+    cache = SimpleNamespace(layers=[state], position=torch.tensor(45, dtype=torch.int64, device=device),
+                            pad_counts=torch.zeros(bs, dtype=torch.int64, device=device))
+    tensors = [state.k_cache, state.v_cache] + [cc.cache for cc in state.conv_caches]
+    saved = [t.clone() for t in tensors]
+    token = torch.randn(bs, 1, d, generator=gen).bfloat16().to(device)
+
+    def restore():
+        for t, s in zip(tensors, saved):
+            t.copy_(s)
+
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream), torch.inference_mode():
+        for _ in range(3):
+            eager = layer(token, cache).clone()
+            after = [t.clone() for t in tensors]
+            restore()
+    torch.cuda.current_stream().wait_stream(stream)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream), torch.inference_mode():
+        out = layer(token, cache)
+    restore()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, eager)
+    assert all(torch.equal(t, a) for t, a in zip(tensors, after))
+    cache.position.add_(1)          # the next token: the replay reads the counter on the device
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.isfinite(out.float()).all() and not torch.equal(out, eager)
+    experts.check_status()
