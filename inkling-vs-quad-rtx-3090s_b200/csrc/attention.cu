@@ -7,7 +7,7 @@
 
 namespace ink {
 
-constexpr int kAttnThreads = 256;
+constexpr int kAttnThreads = 256;   // (128 and 512 threads, i.e. 32 and 128 slots per block, measured the same)
 constexpr int kAttnWarps = kAttnThreads / 32;
 constexpr int kAttnKeys = 8;                                // cache slots a warp scores side by side
 constexpr int kAttnSlots = kAttnWarps * kAttnKeys;          // slots per block: 64
@@ -151,8 +151,10 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(AttnArgs
   __syncthreads();
   // the block's 64 scores: every warp finds the maximum for itself (two scores per lane, five shuffles), the
   // first two warps turn the scores into exponentials once for everybody
-  static_assert(kAttnSlots == 64, "two scores per lane");
-  float top = fmaxf(s_scores[lane], s_scores[lane + 32]);
+  static_assert(kAttnSlots % 32 == 0, "whole scores per lane");
+  float top = s_scores[lane];
+#pragma unroll
+  for (int i = 1; i < kAttnSlots / 32; ++i) top = fmaxf(top, s_scores[lane + 32 * i]);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
   if (tid < kAttnSlots) {
