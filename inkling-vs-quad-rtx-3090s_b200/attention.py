@@ -80,8 +80,8 @@ class DecodeAttention(nn.Module):
 class DecodeLayer(nn.Module):
     """One sparse decoder layer at decode, `MyInklingDecoderLayer.forward` (my_inkling/model.py:661-675):
     h' = attn_sconv(attention(input_norm(h)), residual=h);  out = mlp_sconv(moe(post_norm(h')), residual=h').
-    `attention` is a DecodeAttention, `moe` a FusedMoE; the two short convolutions use the layer's convolution caches
-    2 and 3 of the reference's cache object."""
+    `attention` is a DecodeAttention, `moe` a FusedMoE (a sparse layer) or a DenseMLP (a dense one); the two short
+    convolutions use the layer's convolution caches 2 and 3 of the reference's cache object."""
 
     def __init__(self, attention: DecodeAttention, moe, input_norm_weight, post_norm_weight, attn_taps, mlp_taps, eps: float = 1e-6):
         super().__init__()
@@ -105,5 +105,48 @@ class DecodeLayer(nn.Module):
         layer = cache.layers[self.attention.layer_idx]
         attended = self.attention(self._norm(hidden_states, self.input_norm_weight), cache)
         h = short_conv(attended.contiguous(), self.attn_taps, layer.conv_caches[2].cache, hidden_states.contiguous())
-        block = self.moe.forward_partial(self._norm(h, self.post_norm_weight).view(bs, d))       # FP32 [bs, d], all-reduced
-        return short_conv(block.view(bs, 1, d), self.mlp_taps, layer.conv_caches[3].cache, h)
+        normed = self._norm(h, self.post_norm_weight).view(bs, d)
+        block = self.moe.forward_partial(normed) if hasattr(self.moe, "forward_partial") else self.moe(normed)   # [bs, d], all-reduced
+        return short_conv(block.view(bs, 1, d).contiguous(), self.mlp_taps, layer.conv_caches[3].cache, h)
+
+
+class DenseMLP(nn.Module):
+    """`MyInklingMLP` (my_inkling/model.py:153-171), the block of a dense layer: three library GEMVs,
+    down(silu(gate(x)) * up(x)) * global_scale, BF16 like the reference's; all-reduced over `group` when the rows of
+    gate/up and the columns of down are sliced."""
+
+    def __init__(self, gate_weight, up_weight, down_weight, global_scale, group=None):
+        super().__init__()
+        for name, t in (("gate_weight", gate_weight), ("up_weight", up_weight), ("down_weight", down_weight), ("global_scale", global_scale)):
+            self.register_buffer(name, t.contiguous())
+        self.group = group
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        y = F.linear(F.silu(F.linear(x, self.gate_weight)) * F.linear(x, self.up_weight), self.down_weight) * self.global_scale
+        return y if self.group is None else all_reduce(y, self.group)
+
+
+class DecodeModel(nn.Module):
+    """One decode step of the reference's model, `MyInkling.forward` with a decoding cache (my_inkling/model.py:679-800):
+    normed embedding, the decoder layers, the final norm, the logits (hidden / mup multiplier through the LM head), and
+    the cache's position counter moved on by one token."""
+
+    def __init__(self, embedding, embed_norm_weight, layers, final_norm_weight, lm_head_weight, mup_multiplier: float,
+                 eps: float = 1e-6, unpadded_vocab_size=None):
+        super().__init__()
+        for name, t in (("embedding", embedding), ("embed_norm_weight", embed_norm_weight), ("final_norm_weight", final_norm_weight),
+                        ("lm_head_weight", lm_head_weight)):
+            self.register_buffer(name, t.contiguous())
+        self.layers = nn.ModuleList(layers)
+        self.mup, self.eps, self.unpadded = float(mup_multiplier), eps, unpadded_vocab_size
+
+    def forward(self, input_ids: torch.Tensor, cache) -> torch.Tensor:
+        """input_ids int64 [bs, 1] -> logits BF16 [bs, 1, vocab]."""
+        norm = self.layers[0]._norm
+        hidden = norm(F.embedding(input_ids, self.embedding), self.embed_norm_weight)
+        for layer in self.layers:
+            hidden = layer(hidden, cache)
+        hidden = norm(hidden, self.final_norm_weight) / self.mup
+        logits = F.linear(hidden, self.lm_head_weight)
+        cache.position.add_(1)
+        return logits if self.unpadded is None else logits[..., : self.unpadded]

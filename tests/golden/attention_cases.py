@@ -36,3 +36,32 @@ def layer_weights(c=LAYER):
         k_taps=w(hk * hd, 1, c["conv_k"], std=0.3, dtype=torch.float32), v_taps=w(hk * hd, 1, c["conv_k"], std=0.3, dtype=torch.float32),
         input_norm=near_one(d), post_norm=near_one(d),
         attn_taps=w(d, 1, c["conv_k"], std=0.3, dtype=torch.float32), mlp_taps=w(d, 1, c["conv_k"], std=0.3, dtype=torch.float32))
+
+# A whole (tiny) model for one decode step: normed embedding, a dense sliding-window layer, a sparse full-attention
+# layer (MoE block = cases.LAYER_CASES["mid"]), final norm, LM head.
+MODEL = dict(moe="mid", hidden=1024, vocab=64, dense_intermediate=512, heads=8, kv_heads=4, head_dim=64, window=32, capacity=96,
+             d_rel=16, rel_extent=48, n_floor=8, alpha=0.1, batch=2, pad_counts=[0, 3], prompt=20, record=(0, 13), seed=31,
+             std=0.04, conv_k=4, eps=1e-6, mup=24.0)
+
+
+def model_weights(c=MODEL):
+    """Every weight of the tiny model outside the MoE block, from the seed (generator and tests build the same)."""
+    import torch
+
+    gen = torch.Generator().manual_seed(c["seed"])
+    d = c["hidden"]
+
+    def w(*shape, std=c["std"], dtype=torch.bfloat16):
+        return (torch.randn(*shape, generator=gen) * std).to(dtype)
+
+    def near_one(n):
+        return (1.0 + 0.1 * torch.randn(n, generator=gen)).to(torch.bfloat16)
+
+    layers = []
+    for i, extent in enumerate((c["window"], c["rel_extent"])):       # layer 0 sliding (extent = window), layer 1 full
+        lw = layer_weights(dict(c, seed=c["seed"] + 10 * (i + 1), rel_extent=extent))
+        layers.append(lw)
+    dense = dict(gate=w(c["dense_intermediate"], d), up=w(c["dense_intermediate"], d), down=w(d, c["dense_intermediate"]),
+                 global_scale=torch.ones(1, dtype=torch.bfloat16))
+    return dict(embedding=w(c["vocab"], d, std=1.0), embed_norm=near_one(d), final_norm=near_one(d), lm_head=w(c["vocab"], d),
+                layers=layers, dense=dense)

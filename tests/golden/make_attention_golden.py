@@ -163,10 +163,80 @@ def run_layer() -> None:
             cache.advance(1)
 
 
+def _load_layer(layer, w) -> None:
+    """Weights of one decoder layer outside its MLP / MoE block into the reference's modules."""
+    a = layer.self_attn
+    a.q_proj.weight.copy_(w["q"]); a.k_proj.weight.copy_(w["k"]); a.v_proj.weight.copy_(w["v"]); a.r_proj.weight.copy_(w["r"])
+    a.o_proj.weight.copy_(w["o"]); a.q_norm.weight.copy_(w["q_norm"]); a.k_norm.weight.copy_(w["k_norm"])
+    a.rel_logits_proj.proj.copy_(w["rel_proj"])
+    for conv, taps in ((a.k_sconv, "k_taps"), (a.v_sconv, "v_taps"), (layer.attn_sconv, "attn_taps"), (layer.mlp_sconv, "mlp_taps")):
+        conv.conv1d.float()            # the reference keeps the convolution taps in FP32
+        conv.conv1d.weight.copy_(w[taps])
+    layer.input_layernorm.weight.copy_(w["input_norm"]); layer.post_attention_layernorm.weight.copy_(w["post_norm"])
+    a.fuse_projections()
+
+
+def run_model() -> None:
+    """The reference's whole model (`MyInkling`, my_inkling/model.py:729-800) with two layers -- a dense sliding-window
+    one and a sparse full-attention one -- prefilled and stepped in decode mode: token ids in, logits out, with every
+    cache and convolution history as each recorded step finds them."""
+    import cases
+    import make_golden
+
+    c = ac.MODEL
+    mc = cases.LAYER_CASES[c["moe"]]
+    text = ref_model.InklingTextConfig(
+        hidden_size=c["hidden"], vocab_size=c["vocab"], num_hidden_layers=2, pad_token_id=0,
+        layer_types=["hybrid_sliding", "hybrid"], mlp_layer_types=["dense", "sparse"], intermediate_size=c["dense_intermediate"],
+        moe_intermediate_size=mc["f"], n_routed_experts=mc["experts"], num_experts_per_tok=mc["top_k"],
+        n_shared_experts=mc["n_shared"], route_scale=8.0, rms_norm_eps=c["eps"],
+        num_attention_heads=c["heads"], num_key_value_heads=c["kv_heads"], head_dim=c["head_dim"],
+        swa_num_attention_heads=c["heads"], swa_num_key_value_heads=c["kv_heads"], swa_head_dim=c["head_dim"],
+        sliding_window_size=c["window"], d_rel=c["d_rel"], rel_extent=c["rel_extent"], conv_kernel_size=c["conv_k"],
+        log_scaling_n_floor=c["n_floor"], log_scaling_alpha=c["alpha"], logits_mup_width_multiplier=c["mup"])
+    model = ref_model.MyInkling(ref_model.InklingConfig(text_config=text, hidden_size=c["hidden"], vocab_size=c["vocab"])).bfloat16().eval()
+    w = ac.model_weights(c)
+    p, banks, _ = cases.make_layer(**mc)
+    with torch.no_grad():
+        tower = model.model.language_model
+        tower.embed_tokens.weight.copy_(w["embedding"]); tower.embed_tokens.embed_norm.weight.copy_(w["embed_norm"])
+        tower.norm.weight.copy_(w["final_norm"]); model.lm_head.weight.copy_(w["lm_head"])
+        for layer, lw in zip(tower.layers, w["layers"]):
+            _load_layer(layer, lw)
+        dense = tower.layers[0].mlp
+        dense.gate_proj.weight.copy_(w["dense"]["gate"]); dense.up_proj.weight.copy_(w["dense"]["up"])
+        dense.down_proj.weight.copy_(w["dense"]["down"]); dense.global_scale.copy_(w["dense"]["global_scale"])
+        tower.layers[1].mlp = make_golden.load_reference_moe(mc, p, banks)
+        routed: dict[str, torch.Tensor] = {}
+        tower.layers[1].mlp.gate.register_forward_hook(lambda m, i, o: routed.__setitem__("indices", o[2].detach().clone()))
+        cache = MyInklingCache(text, batch_size=c["batch"], capacity=c["capacity"], pad_counts=torch.tensor(c["pad_counts"]),
+                               dtype=torch.bfloat16, device="cpu")
+        gen = torch.Generator().manual_seed(c["seed"] + 1)
+        model(torch.randint(1, c["vocab"], (c["batch"], c["prompt"]), generator=gen), cache=cache)
+        cache.prepare_decode()
+        for step in range(max(c["record"]) + 1):
+            position = int(cache.position)
+            ids = torch.randint(1, c["vocab"], (c["batch"], 1), generator=gen)
+            if step in c["record"]:
+                for li in range(2):
+                    for i in range(4):
+                        put(f"model/{step}/layer{li}/history{i}", cache.layers[li].conv_caches[i].cache)
+            logits = model(ids, cache=cache)
+            if step in c["record"]:
+                put(f"model/{step}/position", torch.tensor(position))
+                put(f"model/{step}/input_ids", ids)
+                put(f"model/{step}/logits", logits[:, 0])
+                put(f"model/{step}/expert_indices", routed["indices"].reshape(c["batch"], -1))   # the sparse layer's routing
+                for li in range(2):
+                    put(f"model/{step}/layer{li}/k_cache", cache.layers[li].k_cache)      # after the step
+                    put(f"model/{step}/layer{li}/v_cache", cache.layers[li].v_cache)
+
+
 def main() -> None:
     for kind in ac.CASES:
         run(kind)
     run_layer()
+    run_model()
     np.savez_compressed(HERE / "attention.npz", **out)
     print(f"wrote {len(out)} arrays, {sum(a.nbytes for a in out.values()) / 1e6:.2f} MB raw")
 

@@ -282,3 +282,76 @@ def test_the_decoder_layer_replays_in_a_cuda_graph(ib):
     torch.cuda.synchronize()
     assert torch.isfinite(out.float()).all() and not torch.equal(out, eager)
     experts.check_status()
+
+
+@pytest.mark.parametrize("step", ac.MODEL["record"])
+def test_a_decode_step_of_the_whole_model(ib, step):
+    """Token ids in, logits out: `MyInkling.forward` with a decoding cache for a two-layer model (a dense sliding-window
+    layer, a sparse full-attention layer with the log scaling on), against the logits the reference's model produced
+    from the same caches and histories; the position counter moves on by one."""
+    from types import SimpleNamespace
+
+    import numpy as np
+
+    import cases
+    from helpers import banks_to_device, layer_on_device
+    from test_attention_oracle import GOLDEN_DIR
+
+    device = torch.device("cuda", 0)
+    c = ac.MODEL
+    z = np.load(GOLDEN_DIR / "attention.npz")
+
+    def t(name, bf16=True):
+        a = torch.from_numpy(z[f"model/{step}/{name}"].copy())
+        return (a.view(torch.bfloat16) if bf16 else a).to(device)
+
+    def dev(tree):
+        return {k: (dev(v) if isinstance(v, dict) else v.to(device)) for k, v in tree.items()}
+
+    w = ac.model_weights(c)
+    p, banks, _ = cases.make_layer(**cases.LAYER_CASES[c["moe"]])
+    dp = layer_on_device(p, device)
+    experts = ib.ResidentExperts(p["d"], p["f"], None, banks_to_device(banks, device))
+    moe = ib.FusedMoE(dp["router_weight"], dp["router_bias"], dp["global_scale"], p["route_scale"], p["top_k"],
+                      dp["shared_gate"], dp["shared_up"], dp["shared_down"], experts, None)
+    dense = dev(w["dense"])
+    blocks = [ib.DenseMLP(dense["gate"], dense["up"], dense["down"], dense["global_scale"]), moe]
+    layers = []
+    for i, (lw, window) in enumerate(zip(w["layers"], (c["window"], 0))):
+        lw = dev(lw)
+        attention = ib.DecodeAttention(torch.cat([lw["q"], lw["k"], lw["v"], lw["r"]]), lw["o"], lw["q_norm"], lw["k_norm"],
+                                       lw["k_taps"], lw["v_taps"], lw["rel_proj"], layer_idx=i, heads=c["heads"],
+                                       kv_heads=c["kv_heads"], head_dim=c["head_dim"], d_rel=c["d_rel"], window=window,
+                                       log_scaling_n_floor=c["n_floor"], log_scaling_alpha=c["alpha"], eps=c["eps"])
+        layers.append(ib.DecodeLayer(attention, blocks[i], lw["input_norm"], lw["post_norm"], lw["attn_taps"], lw["mlp_taps"], eps=c["eps"]))
+    model = ib.DecodeModel(w["embedding"].to(device), w["embed_norm"].to(device), layers, w["final_norm"].to(device),
+                           w["lm_head"].to(device), c["mup"], eps=c["eps"])
+    position = int(z[f"model/{step}/position"])
+    states = []
+    for li, window in enumerate((c["window"], 0)):
+        slot = position % window if window else position
+        k, v = t(f"layer{li}/k_cache").clone(), t(f"layer{li}/v_cache").clone()
+        k[:, :, slot] = 0
+        v[:, :, slot] = 0
+        states.append(SimpleNamespace(k_cache=k, v_cache=v,
+                                      conv_caches=[SimpleNamespace(cache=t(f"layer{li}/history{i}", False)) for i in range(4)]))
+    cache = SimpleNamespace(layers=states, position=torch.tensor(position, dtype=torch.int64, device=device),
+                            pad_counts=torch.tensor(c["pad_counts"], dtype=torch.int64, device=device))
+    logits = model(t("input_ids", False), cache)
+    torch.cuda.synchronize()
+    experts.check_status()
+    assert int(cache.position) == position + 1
+    got, want = logits[:, 0].float().cpu(), t("logits").float().cpu()
+    assert got.shape == want.shape == (c["batch"], c["vocab"])
+    # The sparse layer's router sees activations that differ from the reference's in the last bits (two layers of
+    # BF16 arithmetic in another order), and a near-tie for the sixth expert can fall the other way: sequences routed
+    # like the reference's are held to the usual bar, the others only to being close (one expert of six differs).
+    mine = moe.topk_indices[: c["batch"]].cpu().sort(-1).values
+    theirs = t("expert_indices", False).cpu().sort(-1).values
+    same = (mine == theirs).all(-1)
+    swapped = sum(len(set(a.tolist()) - set(b.tolist())) for a, b in zip(mine, theirs))
+    assert int(same.sum()) >= 1 and swapped <= 1
+    scale = want.abs().max()
+    assert (got[same] - want[same]).abs().max() <= TOL * scale, float((got[same] - want[same]).abs().max() / scale)
+    assert (got - want).abs().max() <= 0.15 * scale
+    assert torch.equal(got.argmax(-1), want.argmax(-1))          # the same next token
